@@ -17,7 +17,8 @@ _P = c_void_p
 _LIB: Optional[ctypes.CDLL] = None
 
 _SIGNATURES = {
-    "mf_embed": [_P, c_int, _P, _P, c_int, c_int, _P],
+    "mf_embed": [_P, c_int, _P, _P, c_int, c_int, c_float, _P],
+    "mf_unary_act": [_P, _P, c_int, c_longlong, c_int, _P],
     "mf_add_rmsnorm": [_P, _P, c_int, _P, c_float, _P, c_int, _P, c_int, c_int, _P],
     "mf_rope_kv_write": [_P, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P, _P, c_int, c_int, _P, _P, _P,
                          _P, c_int, c_int, _P],
@@ -64,11 +65,11 @@ _SIGNATURES = {
     "mf_delta_gates": [_P, _P, _P, c_int, c_int, c_int, c_int, _P],
     "mf_delta_recurrence": [_P, _P, _P, c_int, _P, c_longlong, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P],
     "mf_delta_output": [_P, _P, c_int, _P, c_float, _P, c_int, c_int, c_int, c_int, _P],
-    "mf_moe_route": [_P, c_int, c_int, c_int, c_int, c_int, c_float, _P, _P, _P],
-    "mf_moe_rows": [_P, _P, _P, c_int, _P, _P, c_int, c_int, c_int, c_int, c_float, c_float, _P],
-    "mf_moe_combine": [_P, c_int, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P],
+    "mf_moe_route": [_P, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, _P, _P, _P, _P],
+    "mf_moe_rows": [_P, _P, _P, c_int, _P, _P, c_int, c_int, c_int, c_int, c_float, c_float, c_float, c_int, _P],
+    "mf_moe_combine": [_P, c_int, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P, c_int, _P, _P, _P, c_int, _P],
     "mf_moe_gather_rows": [_P, _P, _P, c_int, c_int, _P],
-    "mf_moe_activation": [_P, _P, c_int, c_int, c_float, c_float, _P],
+    "mf_moe_activation": [_P, _P, c_int, c_int, c_float, c_float, c_float, _P],
     "mf_moe_rows_slices": [c_int],
     "mf_attention_talking_tc_ok": [c_int, c_int, c_int, c_int, c_int],
     "mf_attention_talking_tc": [_P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P, c_int,
@@ -80,7 +81,7 @@ _SIGNATURES = {
     "mf_moe_sort": [_P, c_int, c_int, c_int, _P, _P, _P, _P, _P, _P],
     "mf_moe_grouped_ok": [c_int, c_int, c_int],
     "mf_moe_grouped_max_tiles": [c_int, c_int, c_int],
-    "mf_moe_grouped_up": [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_float, c_float, _P],
+    "mf_moe_grouped_up": [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_float, _P],
     "mf_moe_grouped_down": [_P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P],
     "mf_attention_prefill_ex": [_P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P, c_int, c_int,
                                 c_float, c_int, c_int, c_int, c_int, _P, _P, c_longlong, _P],
@@ -93,13 +94,14 @@ _SIGNATURES = {
     "mf_rope_store": [_P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P, _P, c_int, c_int, _P, _P, _P, _P,
                       _P, c_int, c_int, _P],
     "mf_latent_prepare": [_P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P, c_float, _P, _P, _P, c_int,
-                          c_int, _P, _P, _P, _P, c_int, _P],
-    "mf_latent_query": [_P, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P, _P, _P, _P],
+                          c_int, _P, _P, _P, _P, c_int, c_int, c_int, c_float, _P],
+    "mf_latent_query": [_P, c_longlong, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P, _P, _P, c_int, c_int,
+                        c_float, _P],
     "mf_head_linear": [_P, c_longlong, c_int, _P, _P, c_longlong, c_int, c_int, c_int, c_int, c_int, c_int, _P,
-                       c_longlong, _P],
+                       c_longlong, c_int, c_int, _P],
     "mf_head_linear_mma_ok": [c_longlong, c_int, c_int],
     "mf_head_linear_mma": [_P, c_longlong, c_int, _P, _P, c_longlong, c_int, c_int, c_int, c_int, c_int, _P,
-                           c_longlong, _P],
+                           c_longlong, c_int, c_int, _P],
     "mf_retention_prepare": [_P, c_int, c_int, c_int, c_int, c_int, c_int, c_float, _P, _P, _P, _P, _P],
     "mf_set_retention_rows": [c_int],
     "mf_retention_parts": [c_int, c_int, c_int, c_longlong],

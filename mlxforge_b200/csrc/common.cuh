@@ -27,11 +27,17 @@ template <typename T> __device__ __forceinline__ T from_f32(float v);
 template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
 template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
 
-// Activations of a gated feed-forward, in 32-bit.
+// Activations of a feed-forward (of its gate, where it has one), in 32-bit.
 #define MF_ACT_SILU 0
 #define MF_ACT_GELU_TANH 1      // 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))
+#define MF_ACT_RELU2 2          // max(z, 0)^2
+#define MF_ACT_COUNT 3
 __device__ __forceinline__ float gate_act(float g, int act) {
   if (act == MF_ACT_GELU_TANH) return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+  if (act == MF_ACT_RELU2) {
+    const float r = fmaxf(g, 0.f);
+    return r * r;
+  }
   return g / (1.0f + expf(-g));
 }
 
@@ -187,6 +193,8 @@ enum MfKernel {
   MF_K_RETENTION_RECURRENCE,  // the decayed state, token after token
   MF_K_RETENTION_CHUNKED,     // the same over runs of tokens as products
   MF_K_RETENTION_OUTPUT,      // per-head norm of the read-out and the gate
+  MF_K_UNARY_ACT,             // an activation applied to every element (a feed-forward without a gate)
+  MF_K_GEMM_TC_ACT,           // many-row product, tcgen05, with that activation in its epilogue
   MF_K_COUNT
 };
 extern unsigned long long g_mf_kernel_launches[MF_K_COUNT];

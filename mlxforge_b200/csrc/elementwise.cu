@@ -15,18 +15,19 @@ MF_API int mf_set_pdl(int on) {
 }
 
 // ------------------------------------------------------------------ embedding
+// out[t] = table[tokens[t]] * scale (scale 1: the row itself)
 template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ tokens,
-                             float* __restrict__ out, int H) {
+                             float* __restrict__ out, int H, float scale) {
   const int t = blockIdx.x;
   const T* row = table + (long long)tokens[t] * H;
   float* o = out + (long long)t * H;
-  for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = to_f32<T>(row[i]);
+  for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = to_f32<T>(row[i]) * scale;
 }
 
 // bfloat16 rows in 16-byte pieces (H a multiple of 8)
 __global__ void embed_bf16_vec_kernel(const __nv_bfloat16* __restrict__ table, const int* __restrict__ tokens,
-                                      float* __restrict__ out, int H) {
+                                      float* __restrict__ out, int H, float scale) {
   pdl_wait();
   pdl_launch();
   const int t = blockIdx.x;
@@ -37,22 +38,22 @@ __global__ void embed_bf16_vec_kernel(const __nv_bfloat16* __restrict__ table, c
     const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
     const float2 a = __bfloat1622float2(p[0]), b = __bfloat1622float2(p[1]);
     const float2 c = __bfloat1622float2(p[2]), d = __bfloat1622float2(p[3]);
-    o[2 * i] = make_float4(a.x, a.y, b.x, b.y);
-    o[2 * i + 1] = make_float4(c.x, c.y, d.x, d.y);
+    o[2 * i] = make_float4(a.x * scale, a.y * scale, b.x * scale, b.y * scale);
+    o[2 * i + 1] = make_float4(c.x * scale, c.y * scale, d.x * scale, d.y * scale);
   }
 }
 
-MF_API int mf_embed(const void* table, int table_dtype, const int* tokens, float* out, int T, int H,
+MF_API int mf_embed(const void* table, int table_dtype, const int* tokens, float* out, int T, int H, float scale,
                     cudaStream_t stream) {
   if (T <= 0) return 0;
   if (table_dtype == MF_BF16 && H % 8 == 0 && ((uintptr_t)table & 15) == 0 && ((uintptr_t)out & 15) == 0) {
     return (int)launch_dep(embed_bf16_vec_kernel, dim3(T), dim3(128), 0, stream, (const __nv_bfloat16*)table, tokens,
-                           out, H);
+                           out, H, scale);
   }
   if (table_dtype == MF_F32)
-    embed_kernel<float><<<T, 256, 0, stream>>>((const float*)table, tokens, out, H);
+    embed_kernel<float><<<T, 256, 0, stream>>>((const float*)table, tokens, out, H, scale);
   else if (table_dtype == MF_BF16)
-    embed_kernel<__nv_bfloat16><<<T, 256, 0, stream>>>((const __nv_bfloat16*)table, tokens, out, H);
+    embed_kernel<__nv_bfloat16><<<T, 256, 0, stream>>>((const __nv_bfloat16*)table, tokens, out, H, scale);
   else
     return MF_ERR_BAD_DTYPE;
   return (int)cudaGetLastError();
@@ -365,7 +366,7 @@ __global__ void swiglu_bf16_g8_kernel(const uint4* __restrict__ gu, uint4* __res
 MF_API int mf_gated_act(const void* gu, void* out, int dtype, int T, int I, int group, int act,
                         cudaStream_t stream) {
   if (T <= 0) return 0;
-  if (group <= 0 || I % group || (act != MF_ACT_SILU && act != MF_ACT_GELU_TANH)) return MF_ERR_BAD_ARG;
+  if (group <= 0 || I % group || act < 0 || act >= MF_ACT_COUNT) return MF_ERR_BAD_ARG;
   if (dtype == MF_BF16 && group == 8 && (((uintptr_t)gu | (uintptr_t)out) & 15) == 0) {
     const long long n_groups = (long long)T * (I / 8);
     swiglu_bf16_g8_kernel<<<(unsigned)((n_groups + 255) / 256), 256, 0, stream>>>((const uint4*)gu, (uint4*)out,
@@ -383,6 +384,52 @@ MF_API int mf_gated_act(const void* gu, void* out, int dtype, int T, int I, int 
   else
     return MF_ERR_BAD_DTYPE;
   return (int)cudaGetLastError();
+}
+
+// ------------------------------------------------------------------ activation without a gate
+// out[i] = act(in[i]) in 32-bit, rounded once (in place where out == in)
+template <typename T>
+__global__ void unary_act_kernel(const T* __restrict__ in, T* __restrict__ out, long long n, int act) {
+  pdl_launch();
+  pdl_wait();
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) out[i] = from_f32<T>(gate_act(to_f32<T>(in[i]), act));
+}
+
+// bfloat16, 8 elements a thread
+__global__ void unary_act_bf16_vec_kernel(const uint4* __restrict__ in, uint4* __restrict__ out, long long n8, int act) {
+  pdl_launch();
+  pdl_wait();
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n8) return;
+  const uint4 v = in[i];
+  const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
+  uint4 o;
+  __nv_bfloat162* q = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+  for (int e = 0; e < 4; e++) {
+    const float2 f = __bfloat1622float2(p[e]);
+    q[e] = __floats2bfloat162_rn(gate_act(f.x, act), gate_act(f.y, act));
+  }
+  out[i] = o;
+}
+
+MF_API int mf_unary_act(const void* in, void* out, int dtype, long long n, int act, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (act < 0 || act >= MF_ACT_COUNT) return MF_ERR_BAD_ARG;
+  mf_count(MF_K_UNARY_ACT);
+  if (dtype == MF_BF16 && n % 8 == 0 && (((uintptr_t)in | (uintptr_t)out) & 15) == 0) {
+    const long long n8 = n / 8;
+    return (int)launch_dep(unary_act_bf16_vec_kernel, dim3((unsigned)((n8 + 255) / 256)), dim3(256), 0, stream,
+                           (const uint4*)in, (uint4*)out, n8, act);
+  }
+  const dim3 grid((unsigned)((n + 255) / 256));
+  if (dtype == MF_F32)
+    return (int)launch_dep(unary_act_kernel<float>, grid, dim3(256), 0, stream, (const float*)in, (float*)out, n, act);
+  if (dtype == MF_BF16)
+    return (int)launch_dep(unary_act_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, (const __nv_bfloat16*)in,
+                           (__nv_bfloat16*)out, n, act);
+  return MF_ERR_BAD_DTYPE;
 }
 
 MF_API int mf_swiglu(const void* gu, void* out, int dtype, int T, int I, int group, cudaStream_t stream) {

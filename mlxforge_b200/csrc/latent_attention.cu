@@ -7,26 +7,54 @@
 // U_v,h applied to the attended latent.  Nothing is ever expanded per cached token.
 //
 //  * latent_prepare: one block per token over a row of projections [dq | dkv | ...]: the RMS norm
-//    of the query latent, the RMS norm of the key/value latent and the half-split rotation of
-//    the shared key part, the last two written into the token's place in the cache.
+//    of the query latent (a model whose queries are projected directly has none: q_rank = 0), the
+//    RMS norm of the key/value latent and the rotation of the shared key part, the last two
+//    written into the token's place in the cache.
 //  * latent_query: the rotated parts of the queries moved (rotated) behind the absorbed parts.
 //  * head_linear: a product per head, out[t, h, :] = W_h x[t, h, :] with W [heads, N, K], rows
-//    and heads of x and out at given strides, optionally times sigmoid(gate); accumulation in
+//    and heads of x and out at given strides, optionally times sigmoid(gate), the gate of output
+//    n of head h read at gate[t * gate_ld + h * gate_hs + n * gate_ns] (one number per channel:
+//    gate_hs = N, gate_ns = 1; one per head: gate_hs = 1, gate_ns = 0); accumulation in
 //    32-bit, a warp per output element.  For few tokens; many tokens take the tensor-core one.
+//
+// The rotation takes its pairing (half-split or adjacent channels), how many of the `rot` channels
+// turn (`rot_dims`, the rest pass unchanged) and a factor on cosine and sine (`mag`; 1 for the plain
+// rotation, the attention factor of a stretched frequency table otherwise) as arguments.
 #include "rotary.cuh"
+
+// dst[0 .. rot) = rotation of src[0 .. rot): the first rot_dims channels turn in pairs, the rest are copied
+template <typename T>
+__device__ __forceinline__ void rotate_part(const T* __restrict__ src, T* __restrict__ dst, int rot, int rot_dims,
+                                            int layout, float mag, int pos, const float* __restrict__ inv_f,
+                                            const double* __restrict__ inv_d, int first, int step) {
+  const int half = rot_dims >> 1;
+  for (int j = first; j < half; j += step) {
+    float c, s;
+    rotary_cs(pos, j, inv_f, inv_d, c, s);
+    c *= mag;
+    s *= mag;
+    int a, b;
+    rotary_pair(layout, rot_dims, j, a, b);
+    const float u = to_f32<T>(src[a]), v = to_f32<T>(src[b]);
+    dst[a] = from_f32<T>(u * c - v * s);
+    dst[b] = from_f32<T>(v * c + u * s);
+  }
+  for (int i = rot_dims + first; i < rot; i += step) dst[i] = src[i];
+}
 
 template <typename T>
 __global__ void latent_prepare_kernel(const T* __restrict__ proj, int ld, int q_rank, int kv_off, int rank, int rot,
                                       const float* __restrict__ wq, const float* __restrict__ wkv, float eps,
                                       const int* __restrict__ positions, const int* __restrict__ seq_of_token,
                                       PagedView pv, const float* __restrict__ inv_f, const double* __restrict__ inv_d,
-                                      T* __restrict__ cq_out, T* __restrict__ k_pool, int write_kv) {
+                                      T* __restrict__ cq_out, T* __restrict__ k_pool, int write_kv, int layout,
+                                      int rot_dims, float mag) {
   __shared__ float red[32];
   pdl_launch();
   pdl_wait();
   const int t = blockIdx.x;
   const T* row = proj + (long long)t * ld;
-  {
+  if (q_rank > 0) {
     float ss = 0.f;
     for (int i = threadIdx.x; i < q_rank; i += blockDim.x) {
       const float v = to_f32<T>(row[i]);
@@ -49,70 +77,65 @@ __global__ void latent_prepare_kernel(const T* __restrict__ proj, int ld, int q_
   ss = block_sum(ss, red);
   const float inv = 1.0f / sqrtf(ss / (float)rank + eps);
   for (int i = threadIdx.x; i < rank; i += blockDim.x) dst[i] = from_f32<T>(to_f32<T>(kv[i]) * inv * wkv[i]);
-  const int half = rot >> 1;
-  for (int j = threadIdx.x; j < half; j += blockDim.x) {
-    float c, s;
-    rotary_cs(pos, j, inv_f, inv_d, c, s);
-    const float u = to_f32<T>(kv[rank + j]), v = to_f32<T>(kv[rank + j + half]);
-    dst[rank + j] = from_f32<T>(u * c - v * s);
-    dst[rank + j + half] = from_f32<T>(v * c + u * s);
-  }
+  rotate_part<T>(kv + rank, dst + rank, rot, rot_dims, layout, mag, pos, inv_f, inv_d, threadIdx.x, blockDim.x);
 }
 
 MF_API int mf_latent_prepare(const void* proj, int dtype, int T, int ld, int q_rank, int kv_off, int rank, int rot,
                              const float* wq, const float* wkv, float eps, const int* positions,
                              const int* seq_of_token, const int* block_table, int bt_stride, int page_size,
                              const float* inv_f, const double* inv_d, void* cq_out, void* k_pool, int write_kv,
-                             cudaStream_t stream) {
+                             int layout, int rot_dims, float mag, cudaStream_t stream) {
   if (T <= 0) return 0;
-  if (q_rank <= 0 || rank <= 0 || rot < 0 || (rot & 1)) return MF_ERR_BAD_ARG;
+  if (q_rank < 0 || rank <= 0 || rot < 0 || rot_dims < 0 || rot_dims > rot || (rot_dims & 1)) return MF_ERR_BAD_ARG;
+  if (layout != MF_ROT_HALF && layout != MF_ROT_PAIRS) return MF_ERR_BAD_ARG;
+  if (q_rank == 0 && !write_kv) return 0;
   PagedView pv{block_table, bt_stride, page_size, 1, rank + rot};
   mf_count(MF_K_LATENT_PREPARE);
   if (dtype == MF_F32)
     return (int)launch_dep(latent_prepare_kernel<float>, dim3(T), dim3(128), 0, stream, (const float*)proj, ld, q_rank,
                            kv_off, rank, rot, wq, wkv, eps, positions, seq_of_token, pv, inv_f, inv_d, (float*)cq_out,
-                           (float*)k_pool, write_kv);
+                           (float*)k_pool, write_kv, layout, rot_dims, mag);
   if (dtype == MF_BF16)
     return (int)launch_dep(latent_prepare_kernel<__nv_bfloat16>, dim3(T), dim3(128), 0, stream,
                            (const __nv_bfloat16*)proj, ld, q_rank, kv_off, rank, rot, wq, wkv, eps, positions,
-                           seq_of_token, pv, inv_f, inv_d, (__nv_bfloat16*)cq_out, (__nv_bfloat16*)k_pool, write_kv);
+                           seq_of_token, pv, inv_f, inv_d, (__nv_bfloat16*)cq_out, (__nv_bfloat16*)k_pool, write_kv,
+                           layout, rot_dims, mag);
   return MF_ERR_BAD_DTYPE;
 }
 
-// q [T, heads, dim + rot] -> q_full[t, h, rank : rank + rot] = rotation of q[t, h, dim : dim + rot]
+// q [T, heads, dim + rot] in rows q_ld apart -> q_full[t, h, rank : rank + rot] = rotation of q[t, h, dim : dim + rot]
 template <typename T>
-__global__ void latent_query_kernel(const T* __restrict__ q, int n_heads, int dim, int rot, int rank,
+__global__ void latent_query_kernel(const T* __restrict__ q, long long q_ld, int n_heads, int dim, int rot, int rank,
                                     const int* __restrict__ positions, const float* __restrict__ inv_f,
-                                    const double* __restrict__ inv_d, T* __restrict__ q_full) {
+                                    const double* __restrict__ inv_d, T* __restrict__ q_full, int layout, int rot_dims,
+                                    float mag) {
   pdl_launch();
   const int t = blockIdx.x;
   const int pos = positions[t];
-  const int half = rot >> 1;
   pdl_wait();
-  for (int idx = threadIdx.x; idx < n_heads * half; idx += blockDim.x) {
-    const int h = idx / half, j = idx - h * half;
-    float c, s;
-    rotary_cs(pos, j, inv_f, inv_d, c, s);
-    const T* src = q + ((long long)t * n_heads + h) * (dim + rot) + dim;
+  // a group of lanes per head: 32 where the block has room for all heads, else the heads take turns
+  const int per = 32, groups = blockDim.x / per, g = threadIdx.x / per, l = threadIdx.x - g * per;
+  for (int h = g; h < n_heads; h += groups) {
+    const T* src = q + t * q_ld + (long long)h * (dim + rot) + dim;
     T* dst = q_full + ((long long)t * n_heads + h) * (rank + rot) + rank;
-    const float u = to_f32<T>(src[j]), v = to_f32<T>(src[j + half]);
-    dst[j] = from_f32<T>(u * c - v * s);
-    dst[j + half] = from_f32<T>(v * c + u * s);
+    rotate_part<T>(src, dst, rot, rot_dims, layout, mag, pos, inv_f, inv_d, l, per);
   }
 }
 
-MF_API int mf_latent_query(const void* q, int dtype, int T, int n_heads, int dim, int rot, int rank,
-                           const int* positions, const float* inv_f, const double* inv_d, void* q_full,
-                           cudaStream_t stream) {
+MF_API int mf_latent_query(const void* q, long long q_ld, int dtype, int T, int n_heads, int dim, int rot, int rank,
+                           const int* positions, const float* inv_f, const double* inv_d, void* q_full, int layout,
+                           int rot_dims, float mag, cudaStream_t stream) {
   if (T <= 0 || rot == 0) return 0;
-  if (rot < 0 || (rot & 1)) return MF_ERR_BAD_ARG;
+  if (rot < 0 || rot_dims < 0 || rot_dims > rot || (rot_dims & 1)) return MF_ERR_BAD_ARG;
+  if (layout != MF_ROT_HALF && layout != MF_ROT_PAIRS) return MF_ERR_BAD_ARG;
   mf_count(MF_K_LATENT_QUERY);
   if (dtype == MF_F32)
-    return (int)launch_dep(latent_query_kernel<float>, dim3(T), dim3(128), 0, stream, (const float*)q, n_heads, dim,
-                           rot, rank, positions, inv_f, inv_d, (float*)q_full);
+    return (int)launch_dep(latent_query_kernel<float>, dim3(T), dim3(128), 0, stream, (const float*)q, q_ld, n_heads,
+                           dim, rot, rank, positions, inv_f, inv_d, (float*)q_full, layout, rot_dims, mag);
   if (dtype == MF_BF16)
     return (int)launch_dep(latent_query_kernel<__nv_bfloat16>, dim3(T), dim3(128), 0, stream, (const __nv_bfloat16*)q,
-                           n_heads, dim, rot, rank, positions, inv_f, inv_d, (__nv_bfloat16*)q_full);
+                           q_ld, n_heads, dim, rot, rank, positions, inv_f, inv_d, (__nv_bfloat16*)q_full, layout,
+                           rot_dims, mag);
   return MF_ERR_BAD_DTYPE;
 }
 
@@ -122,7 +145,8 @@ constexpr int HL_WARPS = 8;
 template <typename T>
 __global__ void __launch_bounds__(HL_WARPS * 32)
 head_linear_kernel(const T* __restrict__ x, long long x_ld, int x_hs, const T* __restrict__ w, T* __restrict__ out,
-                   long long out_ld, int out_hs, int N, int K, const T* __restrict__ gate, long long gate_ld) {
+                   long long out_ld, int out_hs, int N, int K, const T* __restrict__ gate, long long gate_ld, int gate_hs,
+                   int gate_ns) {
   extern __shared__ float xs[];          // [K]
   pdl_launch();
   pdl_wait();
@@ -133,14 +157,14 @@ head_linear_kernel(const T* __restrict__ x, long long x_ld, int x_hs, const T* _
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const T* wh = w + (long long)h * N * K;
   T* orow = out + t * out_ld + (long long)h * out_hs;
-  const T* grow = gate ? gate + t * gate_ld + (long long)h * N : nullptr;
+  const T* grow = gate ? gate + t * gate_ld + (long long)h * gate_hs : nullptr;
   for (int n = warp; n < N; n += HL_WARPS) {
     const T* wr = wh + (long long)n * K;
     float acc = 0.f;
     for (int k = lane; k < K; k += 32) acc = fmaf(xs[k], to_f32<T>(wr[k]), acc);
     acc = warp_sum(acc);
     if (lane == 0) {
-      if (grow) acc *= 1.0f / (1.0f + expf(-to_f32<T>(grow[n])));
+      if (grow) acc *= 1.0f / (1.0f + expf(-to_f32<T>(grow[n * gate_ns])));
       orow[n] = from_f32<T>(acc);
     }
   }
@@ -174,7 +198,7 @@ __device__ __forceinline__ void hm_mma(float (&c)[4], const unsigned (&a)[4], un
 __global__ void __launch_bounds__(HM_WARPS * 32)
 head_linear_mma_kernel(const __nv_bfloat16* __restrict__ x, long long x_ld, int x_hs, const __nv_bfloat16* __restrict__ w,
                        __nv_bfloat16* __restrict__ out, long long out_ld, int out_hs, int T, int N, int K,
-                       const __nv_bfloat16* __restrict__ gate, long long gate_ld) {
+                       const __nv_bfloat16* __restrict__ gate, long long gate_ld, int gate_hs, int gate_ns) {
   extern __shared__ __align__(16) unsigned char hm_smem[];
   const int ld = K + 8, chunks = K >> 3;
   __nv_bfloat16* x_s = reinterpret_cast<__nv_bfloat16*>(hm_smem);      // [HM_BM][ld]
@@ -216,7 +240,7 @@ head_linear_mma_kernel(const __nv_bfloat16* __restrict__ x, long long x_ld, int 
     const int t = t0 + warp * 16 + g + hh * 8;
     if (t >= T) continue;
     __nv_bfloat16* orow = out + t * out_ld + (long long)h * out_hs;
-    const __nv_bfloat16* grow = gate ? gate + t * gate_ld + (long long)h * N : nullptr;
+    const __nv_bfloat16* grow = gate ? gate + t * gate_ld + (long long)h * gate_hs : nullptr;
 #pragma unroll
     for (int j = 0; j < HM_BN / 8; j++) {
 #pragma unroll
@@ -224,7 +248,7 @@ head_linear_mma_kernel(const __nv_bfloat16* __restrict__ x, long long x_ld, int 
         const int n = n0 + j * 8 + tq * 2 + e;
         if (n < N) {
           float v = acc[j][hh * 2 + e];
-          if (grow) v *= 1.0f / (1.0f + __expf(-__bfloat162float(grow[n])));
+          if (grow) v *= 1.0f / (1.0f + __expf(-__bfloat162float(grow[n * gate_ns])));
           orow[n] = __float2bfloat16_rn(v);
         }
       }
@@ -240,7 +264,7 @@ MF_API int mf_head_linear_mma_ok(long long x_ld, int x_hs, int K) {
 
 MF_API int mf_head_linear_mma(const void* x, long long x_ld, int x_hs, const void* w, void* out, long long out_ld,
                               int out_hs, int T, int n_heads, int N, int K, const void* gate, long long gate_ld,
-                              cudaStream_t stream) {
+                              int gate_hs, int gate_ns, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (!mf_head_linear_mma_ok(x_ld, x_hs, K) || n_heads <= 0 || n_heads > 65535 || N <= 0) return MF_ERR_BAD_ARG;
   if (((uintptr_t)x | (uintptr_t)w) & 15) return MF_ERR_BAD_ARG;
@@ -257,12 +281,12 @@ MF_API int mf_head_linear_mma(const void* x, long long x_ld, int x_hs, const voi
   dim3 grid((T + HM_BM - 1) / HM_BM, n_heads, (N + HM_BN - 1) / HM_BN);
   return (int)launch_dep(head_linear_mma_kernel, grid, dim3(HM_WARPS * 32), smem, stream, (const __nv_bfloat16*)x, x_ld,
                          x_hs, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, out_ld, out_hs, T, N, K,
-                         (const __nv_bfloat16*)gate, gate_ld);
+                         (const __nv_bfloat16*)gate, gate_ld, gate_hs, gate_ns);
 }
 
 MF_API int mf_head_linear(const void* x, long long x_ld, int x_hs, const void* w, void* out, long long out_ld,
                           int out_hs, int dtype, int T, int n_heads, int N, int K, const void* gate,
-                          long long gate_ld, cudaStream_t stream) {
+                          long long gate_ld, int gate_hs, int gate_ns, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (n_heads <= 0 || n_heads > 65535 || N <= 0 || K <= 0 || K > 8192) return MF_ERR_BAD_ARG;
   const size_t smem = (size_t)K * sizeof(float);
@@ -270,10 +294,10 @@ MF_API int mf_head_linear(const void* x, long long x_ld, int x_hs, const void* w
   if (dtype == MF_F32)
     return (int)launch_dep(head_linear_kernel<float>, dim3(T, n_heads), dim3(HL_WARPS * 32), smem, stream,
                            (const float*)x, x_ld, x_hs, (const float*)w, (float*)out, out_ld, out_hs, N, K,
-                           (const float*)gate, gate_ld);
+                           (const float*)gate, gate_ld, gate_hs, gate_ns);
   if (dtype == MF_BF16)
     return (int)launch_dep(head_linear_kernel<__nv_bfloat16>, dim3(T, n_heads), dim3(HL_WARPS * 32), smem, stream,
                            (const __nv_bfloat16*)x, x_ld, x_hs, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, out_ld,
-                           out_hs, N, K, (const __nv_bfloat16*)gate, gate_ld);
+                           out_hs, N, K, (const __nv_bfloat16*)gate, gate_ld, gate_hs, gate_ns);
   return MF_ERR_BAD_DTYPE;
 }

@@ -1,15 +1,20 @@
 // Mixture of experts: the router's choice and the experts' feed-forward.
 //
-// Router (32-bit): s = sigmoid(z) over E experts.  The experts form `n_groups` equal groups of
-// neighbours; a group's score is the sum of its two largest s, and only experts of the `keep`
-// best groups can be chosen (n_groups = 0: no such limit).  The `top` largest s among the
-// allowed experts are chosen; their weights are s * route_scale, not renormalised.  Ties go to
-// the lower index.
+// Router (32-bit): s = sigmoid(z) over E experts, or s = softmax(z) over them (`mode`).  The
+// experts form `n_groups` equal groups of neighbours; a group's score is the sum of its two
+// largest s, and only experts of the `keep` best groups can be chosen (n_groups = 0: no such
+// limit).  The `top` allowed experts with the largest s + bias (`bias`: one number per expert
+// that only steers the choice; none: s itself) are chosen; their weights are s * route_scale,
+// without the bias and not renormalised.  Ties go to the lower index.
 //
 // Expert:  g = min(Wg x, limit),  u = clamp(Wu x, -limit, limit),
-//          y = Wd ( g * sigmoid(alpha g) * (u + 1) )
+//          y = Wd ( g * sigmoid(alpha g) * (u + up_off) )
 // with the weights of all experts stacked: w_gu [E, 2, ff, H] (gate rows, then up rows) and
-// w_down [E, H, ff].
+// w_down [E, H, ff].  (limit = infinity, alpha = 1, up_off = 0: the plain SiLU-gated expert.)
+//
+// Identity experts: router outputs from `n_real` on have no matrices; such an expert returns its
+// input.  The experts' kernels skip them and the weighted sum adds weight * x for them.  The sum
+// can also add a shared branch that every token takes: sigmoid(gate logit of the token) * shared.
 //
 // mf_moe_rows is the kernel for few tokens and for the 32-bit path: a block per (token, chosen
 // expert, slice of the expert's columns) streams its part of that expert's matrices once; the
@@ -22,8 +27,8 @@ __device__ __forceinline__ float moe_sigmoid(float x) { return 1.0f / (1.0f + ex
 // ------------------------------------------------------------------ router
 // one warp per token; dynamic shared memory per warp: s[E], sel[E], gs[n_groups]
 __global__ void __launch_bounds__(128)
-moe_route_kernel(const float* __restrict__ z, int E, int n_groups, int keep, int top, float route_scale,
-                 int* __restrict__ ids, float* __restrict__ weights, int T) {
+moe_route_kernel(const float* __restrict__ z, int ldz, int E, int n_groups, int keep, int top, float route_scale,
+                 int mode, const float* __restrict__ bias, int* __restrict__ ids, float* __restrict__ weights, int T) {
   extern __shared__ float sm[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x * (blockDim.x >> 5) + warp;
@@ -32,10 +37,22 @@ moe_route_kernel(const float* __restrict__ z, int E, int n_groups, int keep, int
   float* s = sm + warp * per_warp;
   float* sel = s + E;
   float* gs = sel + E;
-  for (int e = lane; e < E; e += 32) {
-    s[e] = moe_sigmoid(z[(long long)t * E + e]);
-    sel[e] = s[e];
+  const float* zr = z + (long long)t * ldz;
+  if (mode == 1) {
+    float m = -INFINITY;
+    for (int e = lane; e < E; e += 32) m = fmaxf(m, zr[e]);
+    m = warp_max(m);
+    float sum = 0.f;
+    for (int e = lane; e < E; e += 32) {
+      s[e] = expf(zr[e] - m);
+      sum += s[e];
+    }
+    sum = warp_sum(sum);
+    for (int e = lane; e < E; e += 32) s[e] = s[e] / sum;
+  } else {
+    for (int e = lane; e < E; e += 32) s[e] = moe_sigmoid(zr[e]);
   }
+  for (int e = lane; e < E; e += 32) sel[e] = bias ? s[e] + bias[e] : s[e];
   __syncwarp();
   if (n_groups > 0) {
     const int per = E / n_groups;
@@ -90,17 +107,18 @@ moe_route_kernel(const float* __restrict__ z, int E, int n_groups, int keep, int
   }
 }
 
-MF_API int mf_moe_route(const float* z, int T, int E, int n_groups, int keep, int top, float route_scale, int* ids,
-                        float* weights, cudaStream_t stream) {
+MF_API int mf_moe_route(const float* z, int ldz, int T, int E, int n_groups, int keep, int top, float route_scale,
+                        int mode, const float* bias, int* ids, float* weights, cudaStream_t stream) {
   if (T <= 0) return 0;
-  if (E <= 0 || top <= 0 || top > E) return MF_ERR_BAD_ARG;
+  if (E <= 0 || top <= 0 || top > E || ldz < E || mode < 0 || mode > 1) return MF_ERR_BAD_ARG;
   if (n_groups > 0 && (E % n_groups || keep < 1 || keep > n_groups || (long long)keep * (E / n_groups) < top))
     return MF_ERR_BAD_ARG;
   const int per_warp = 2 * E + (n_groups > 0 ? n_groups : 1);
   const size_t smem = (size_t)4 * per_warp * sizeof(float);
   if (smem > 48 * 1024) return MF_ERR_BAD_ARG;
   mf_count(MF_K_MOE_ROUTE);
-  moe_route_kernel<<<(T + 3) / 4, 128, smem, stream>>>(z, E, n_groups, keep, top, route_scale, ids, weights, T);
+  moe_route_kernel<<<(T + 3) / 4, 128, smem, stream>>>(z, ldz, E, n_groups, keep, top, route_scale, mode, bias, ids,
+                                                       weights, T);
   return (int)cudaGetLastError();
 }
 
@@ -113,7 +131,8 @@ MF_API int mf_moe_route(const float* z, int T, int E, int n_groups, int keep, in
 template <typename T>
 __global__ void __launch_bounds__(256)
 moe_rows_kernel(const T* __restrict__ x, const T* __restrict__ w_gu, const T* __restrict__ w_down,
-                const int* __restrict__ ids, float* __restrict__ y, int H, int ff, int top, float limit, float alpha) {
+                const int* __restrict__ ids, float* __restrict__ y, int H, int ff, int top, float limit, float alpha,
+                float up_off, int n_real) {
   extern __shared__ float sm[];
   float* xs = sm;            // [H]
   float* act = sm + H;       // [MOE_SLICE]
@@ -122,6 +141,7 @@ moe_rows_kernel(const T* __restrict__ x, const T* __restrict__ w_gu, const T* __
   const int t = blockIdx.x, k = blockIdx.y, slice = blockIdx.z;
   const int f0 = slice * MOE_SLICE, fn = min(MOE_SLICE, ff - f0);
   const int e = ids[(long long)t * top + k];
+  if (e >= n_real) return;     // an identity expert: the weighted sum takes the input itself
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
   for (int i = threadIdx.x; i < H; i += blockDim.x) xs[i] = to_f32<T>(x[(long long)t * H + i]);
   __syncthreads();
@@ -141,7 +161,7 @@ moe_rows_kernel(const T* __restrict__ x, const T* __restrict__ w_gu, const T* __
       g = fminf(g, limit);
       u = fminf(fmaxf(u, -limit), limit);
       // the activation is rounded where a product in the compute dtype would read it
-      act[f] = to_f32<T>(from_f32<T>(g * moe_sigmoid(alpha * g) * (u + 1.0f)));
+      act[f] = to_f32<T>(from_f32<T>(g * moe_sigmoid(alpha * g) * (u + up_off)));
     }
   }
   __syncthreads();
@@ -173,7 +193,7 @@ __device__ __forceinline__ float moe_dot8(const uint4 w, const float* xv) {
 __global__ void __launch_bounds__(256)
 moe_rows_bf16_vec_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w_gu,
                          const __nv_bfloat16* __restrict__ w_down, const int* __restrict__ ids, float* __restrict__ y,
-                         int H, int ff, int top, float limit, float alpha) {
+                         int H, int ff, int top, float limit, float alpha, float up_off, int n_real) {
   extern __shared__ __align__(16) float sm[];
   float* xs = sm;            // [H]
   float* act = sm + H;       // [MOE_SLICE]
@@ -182,6 +202,7 @@ moe_rows_bf16_vec_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat1
   const int t = blockIdx.x, k = blockIdx.y, slice = blockIdx.z;
   const int f0 = slice * MOE_SLICE, fn = min(MOE_SLICE, ff - f0);
   const int e = ids[(long long)t * top + k];
+  if (e >= n_real) return;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
   for (int i = threadIdx.x; i < H; i += blockDim.x) xs[i] = __bfloat162float(x[(long long)t * H + i]);
   if (threadIdx.x < MOE_SLICE) act[threadIdx.x] = 0.f;
@@ -205,7 +226,7 @@ moe_rows_bf16_vec_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat1
     if (lane == 0) {
       g = fminf(g, limit);
       u = fminf(fmaxf(u, -limit), limit);
-      act[f] = __bfloat162float(__float2bfloat16_rn(g * moe_sigmoid(alpha * g) * (u + 1.0f)));
+      act[f] = __bfloat162float(__float2bfloat16_rn(g * moe_sigmoid(alpha * g) * (u + up_off)));
     }
   }
   __syncthreads();
@@ -228,7 +249,8 @@ moe_rows_bf16_vec_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat1
 MF_API int mf_moe_rows_slices(int ff) { return (ff + MOE_SLICE - 1) / MOE_SLICE; }
 
 MF_API int mf_moe_rows(const void* x, const void* w_gu, const void* w_down, int dtype, const int* ids, float* y, int T,
-                       int H, int ff, int top, float limit, float alpha, cudaStream_t stream) {
+                       int H, int ff, int top, float limit, float alpha, float up_off, int n_real,
+                       cudaStream_t stream) {
   if (T <= 0) return 0;
   const size_t smem = (size_t)(H + MOE_SLICE) * sizeof(float);
   if (smem > 200 * 1024 || top > 65535) return MF_ERR_BAD_ARG;
@@ -241,7 +263,7 @@ MF_API int mf_moe_rows(const void* x, const void* w_gu, const void* w_down, int 
       if (e != cudaSuccess) return (int)e;                                                                         \
     }                                                                                                              \
     return (int)launch_dep(KERNEL, grid, dim3(256), smem, stream, (const TT*)x, (const TT*)w_gu, (const TT*)w_down, \
-                           ids, y, H, ff, top, limit, alpha);                                                      \
+                           ids, y, H, ff, top, limit, alpha, up_off, n_real);                                      \
   } while (0)
   if (dtype == MF_F32) MR_LAUNCH(moe_rows_kernel<float>, float);
   if (dtype == MF_BF16) {
@@ -256,22 +278,41 @@ MF_API int mf_moe_rows(const void* x, const void* w_gu, const void* w_down, int 
 // ------------------------------------------------------------------ the weighted sum of the chosen experts
 // out[t] = sum_k weights[t, k] * sum_s y[src(t, k) * slices + s], k in the order of the choice,
 // the slices of an expert in their order.  `slot_of` null: src(t, k) = t * top + k; else the row
-// of y that holds the pair (tokens sorted by expert).
+// of y that holds the pair (tokens sorted by expert).  With `ids` and `x`: a chosen expert from
+// `n_real` on is an identity expert, whose output is x[t].  With `shared`: the token's row of it,
+// times sigmoid(shared_gate[t * gate_ld]) where a gate is given, is added last.
+struct MoeExtras {
+  const int* ids;
+  int n_real;
+  const void* x;
+  const void* shared;
+  const float* shared_gate;
+  int gate_ld;
+};
+
 template <typename TO, typename TY>
 __global__ void __launch_bounds__(256)
 moe_combine_kernel(const TY* __restrict__ y, const float* __restrict__ weights, const int* __restrict__ slot_of,
-                   TO* __restrict__ out, int H, int top, int slices) {
+                   TO* __restrict__ out, int H, int top, int slices, MoeExtras ex) {
   pdl_launch();
   pdl_wait();
   const int t = blockIdx.x;
+  const TO* x = reinterpret_cast<const TO*>(ex.x);
+  const TO* shared = reinterpret_cast<const TO*>(ex.shared);
+  const float sg = shared ? (ex.shared_gate ? moe_sigmoid(ex.shared_gate[(long long)t * ex.gate_ld]) : 1.0f) : 0.f;
   for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < H; i += gridDim.y * blockDim.x) {
     float a = 0.f;
     for (int k = 0; k < top; k++) {
-      const long long row = (slot_of ? slot_of[(long long)t * top + k] : (long long)t * top + k) * slices;
       float part = 0.f;
-      for (int sl = 0; sl < slices; sl++) part += to_f32<TY>(y[(row + sl) * H + i]);
+      if (ex.ids && ex.ids[(long long)t * top + k] >= ex.n_real) {
+        part = to_f32<TO>(x[(long long)t * H + i]);
+      } else {
+        const long long row = (slot_of ? slot_of[(long long)t * top + k] : (long long)t * top + k) * slices;
+        for (int sl = 0; sl < slices; sl++) part += to_f32<TY>(y[(row + sl) * H + i]);
+      }
       a = fmaf(weights[(long long)t * top + k], part, a);
     }
+    if (shared) a = fmaf(sg, to_f32<TO>(shared[(long long)t * H + i]), a);
     out[(long long)t * H + i] = from_f32<TO>(a);
   }
 }
@@ -306,17 +347,20 @@ moe_combine_bf16_vec_kernel(const __nv_bfloat16* __restrict__ y, const float* __
 }
 
 MF_API int mf_moe_combine(const void* y, int y_dtype, const float* weights, const int* slot_of, void* out, int out_dtype,
-                          int T, int H, int top, int slices, cudaStream_t stream) {
+                          int T, int H, int top, int slices, const int* ids, int n_real, const void* x,
+                          const void* shared, const float* shared_gate, int gate_ld, cudaStream_t stream) {
   if (T <= 0) return 0;
+  if (ids && !x) return MF_ERR_BAD_ARG;
+  const MoeExtras ex{ids, n_real, x, shared, shared_gate, gate_ld};
   mf_count(MF_K_MOE_COMBINE);
-  if (y_dtype == MF_BF16 && out_dtype == MF_BF16 && slices == 1 && H % 8 == 0 && ((uintptr_t)y & 15) == 0 &&
+  if (!ids && !shared && y_dtype == MF_BF16 && out_dtype == MF_BF16 && slices == 1 && H % 8 == 0 && ((uintptr_t)y & 15) == 0 &&
       ((uintptr_t)out & 15) == 0)
     return (int)launch_dep(moe_combine_bf16_vec_kernel, dim3(T, (H / 8 + 255) / 256), dim3(256), 0, stream,
                            (const __nv_bfloat16*)y, weights, slot_of, (__nv_bfloat16*)out, H, top);
   const dim3 grid(T, (H + 255) / 256);
 #define MC_LAUNCH(TO, TY)                                                                                       \
   return (int)launch_dep(moe_combine_kernel<TO, TY>, grid, dim3(256), 0, stream, (const TY*)y, weights, slot_of, \
-                         (TO*)out, H, top, slices)
+                         (TO*)out, H, top, slices, ex)
   if (y_dtype == MF_F32 && out_dtype == MF_F32) MC_LAUNCH(float, float);
   if (y_dtype == MF_F32 && out_dtype == MF_BF16) MC_LAUNCH(__nv_bfloat16, float);
   if (y_dtype == MF_BF16 && out_dtype == MF_BF16) MC_LAUNCH(__nv_bfloat16, __nv_bfloat16);

@@ -4,6 +4,8 @@
 //
 //   mf_moe_sort     one block: counts per expert, offsets, a row for every pair (slot_of), the
 //                   token of every row (row_token), and the list of tiles (expert, first row, rows).
+//                   Pairs whose expert is `n_real` or above (identity experts, which have no
+//                   matrices) get no row: slot_of is -1 for them.
 //                   Which row a pair gets inside its expert's range is not fixed, and need not be:
 //                   every row is computed by itself, and the sum over a token's experts is taken in
 //                   the order of the choice by the combine kernel.
@@ -44,7 +46,8 @@ moe_sort_kernel(const int* __restrict__ ids, int n_pairs, int E, int top, int* _
   __shared__ int count[MG_MAX_EXPERTS], offset[MG_MAX_EXPERTS], cursor[MG_MAX_EXPERTS];
   for (int e = threadIdx.x; e < E; e += blockDim.x) count[e] = cursor[e] = 0;
   __syncthreads();
-  for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) atomicAdd(&count[ids[i]], 1);
+  for (int i = threadIdx.x; i < n_pairs; i += blockDim.x)
+    if (ids[i] < E) atomicAdd(&count[ids[i]], 1);
   __syncthreads();
   if (threadIdx.x == 0) {
     int off = 0, nt = 0;
@@ -64,10 +67,18 @@ moe_sort_kernel(const int* __restrict__ ids, int n_pairs, int E, int top, int* _
   __syncthreads();
   for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) {
     const int e = ids[i];
+    if (e >= E) {                     // an identity expert: no row
+      slot_of[i] = -1;
+      continue;
+    }
     const int row = offset[e] + atomicAdd(&cursor[e], 1);
     slot_of[i] = row;
     row_token[row] = i / top;
   }
+  // rows that no pair took (pairs of identity experts have none) name token 0, so that a gather over all
+  // n_pairs rows stays inside x
+  const int used = offset[E - 1] + count[E - 1];
+  for (int i = used + threadIdx.x; i < n_pairs; i += blockDim.x) row_token[i] = 0;
 }
 
 MF_API int mf_moe_sort(const int* ids, int T, int E, int top, int* slot_of, int* row_token, int* meta, int* tiles,
@@ -148,7 +159,7 @@ __device__ __forceinline__ void mg_tile(float (&acc)[NB][MG_BN / 8][4], int K, A
 __global__ void __launch_bounds__(128)
 moe_grouped_up_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w_gu,
                       const int* __restrict__ row_token, const int* __restrict__ meta, const int* __restrict__ tiles,
-                      __nv_bfloat16* __restrict__ act, int H, int ff, float limit, float alpha) {
+                      __nv_bfloat16* __restrict__ act, int H, int ff, float limit, float alpha, float up_off) {
   extern __shared__ __align__(16) __nv_bfloat16 mg_smem[];
   __nv_bfloat16* As = mg_smem;
   __nv_bfloat16* Bs = mg_smem + MG_STAGES * MG_BM * MG_LD;
@@ -185,7 +196,7 @@ moe_grouped_up_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* 
       for (int j = 0; j < 2; j++) {
         const float g = fminf(acc[0][nt][half * 2 + j], limit);
         const float u = fminf(fmaxf(acc[1][nt][half * 2 + j], -limit), limit);
-        v[j] = g * (1.0f / (1.0f + __expf(-alpha * g))) * (u + 1.0f);
+        v[j] = g * (1.0f / (1.0f + __expf(-alpha * g))) * (u + up_off);
       }
       *reinterpret_cast<__nv_bfloat162*>(act + (long long)(row_first + r) * ff + col) = __floats2bfloat162_rn(v[0], v[1]);
     }
@@ -230,7 +241,7 @@ MF_API int mf_moe_grouped_ok(int H, int ff, int E) {
 MF_API int mf_moe_grouped_max_tiles(int T, int top, int E) { return (T * top + MG_BM - 1) / MG_BM + E; }
 
 MF_API int mf_moe_grouped_up(const void* x, const void* w_gu, const int* row_token, const int* meta, const int* tiles,
-                             void* act, int T, int H, int ff, int E, int top, float limit, float alpha,
+                             void* act, int T, int H, int ff, int E, int top, float limit, float alpha, float up_off,
                              cudaStream_t stream) {
   if (T <= 0) return 0;
   if (!mf_moe_grouped_ok(H, ff, E)) return MF_ERR_BAD_ARG;
@@ -246,7 +257,7 @@ MF_API int mf_moe_grouped_up(const void* x, const void* w_gu, const int* row_tok
     once.done[dev] = true;
   }
   moe_grouped_up_kernel<<<grid, 128, smem, stream>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w_gu, row_token, meta,
-                                                  tiles, (__nv_bfloat16*)act, H, ff, limit, alpha);
+                                                  tiles, (__nv_bfloat16*)act, H, ff, limit, alpha, up_off);
   return (int)cudaGetLastError();
 }
 
@@ -279,23 +290,23 @@ MF_API int mf_moe_gather_rows(const void* x, const int* row_token, void* xg, int
   return (int)cudaGetLastError();
 }
 
-// act[r, f] = g sigmoid(alpha g) (u + 1), g = min(gu[r, f], limit), u = clamp(gu[r, ff + f], -limit, limit)
+// act[r, f] = g sigmoid(alpha g) (u + up_off), g = min(gu[r, f], limit), u = clamp(gu[r, ff + f], -limit, limit)
 __global__ void __launch_bounds__(256)
 moe_activation_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ act, int ff, float limit,
-                      float alpha, long long total) {
+                      float alpha, float up_off, long long total) {
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= total) return;
   const long long r = i / ff;
   const int f = (int)(i - r * ff);
   const float g = fminf(__bfloat162float(gu[r * 2 * ff + f]), limit);
   const float u = fminf(fmaxf(__bfloat162float(gu[r * 2 * ff + ff + f]), -limit), limit);
-  act[i] = __float2bfloat16_rn(g * (1.0f / (1.0f + __expf(-alpha * g))) * (u + 1.0f));
+  act[i] = __float2bfloat16_rn(g * (1.0f / (1.0f + __expf(-alpha * g))) * (u + up_off));
 }
 
 // the same, 8 columns a thread (ff a multiple of 8)
 __global__ void __launch_bounds__(256)
 moe_activation_vec_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ act, int ff, float limit,
-                          float alpha, long long total8) {
+                          float alpha, float up_off, long long total8) {
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= total8) return;
   const int f8 = ff / 8;
@@ -312,13 +323,13 @@ moe_activation_vec_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* _
     const float2 g2 = __bfloat1622float2(gp[j]), u2 = __bfloat1622float2(up[j]);
     const float g0 = fminf(g2.x, limit), g1 = fminf(g2.y, limit);
     const float u0 = fminf(fmaxf(u2.x, -limit), limit), u1 = fminf(fmaxf(u2.y, -limit), limit);
-    op[j] = __floats2bfloat162_rn(g0 * (1.0f / (1.0f + __expf(-alpha * g0))) * (u0 + 1.0f),
-                                  g1 * (1.0f / (1.0f + __expf(-alpha * g1))) * (u1 + 1.0f));
+    op[j] = __floats2bfloat162_rn(g0 * (1.0f / (1.0f + __expf(-alpha * g0))) * (u0 + up_off),
+                                  g1 * (1.0f / (1.0f + __expf(-alpha * g1))) * (u1 + up_off));
   }
   *reinterpret_cast<uint4*>(act + r * ff + f) = o;
 }
 
-MF_API int mf_moe_activation(const void* gu, void* act, int n_rows, int ff, float limit, float alpha,
+MF_API int mf_moe_activation(const void* gu, void* act, int n_rows, int ff, float limit, float alpha, float up_off,
                              cudaStream_t stream) {
   if (n_rows <= 0) return 0;
   const long long total = (long long)n_rows * ff;
@@ -326,10 +337,10 @@ MF_API int mf_moe_activation(const void* gu, void* act, int n_rows, int ff, floa
   if (ff % 8 == 0 && ((uintptr_t)gu & 15) == 0 && ((uintptr_t)act & 15) == 0) {
     const long long total8 = total / 8;
     moe_activation_vec_kernel<<<(unsigned)((total8 + 255) / 256), 256, 0, stream>>>(
-        (const __nv_bfloat16*)gu, (__nv_bfloat16*)act, ff, limit, alpha, total8);
+        (const __nv_bfloat16*)gu, (__nv_bfloat16*)act, ff, limit, alpha, up_off, total8);
     return (int)cudaGetLastError();
   }
   moe_activation_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>((const __nv_bfloat16*)gu,
-                                                                             (__nv_bfloat16*)act, ff, limit, alpha, total);
+                                                                             (__nv_bfloat16*)act, ff, limit, alpha, up_off, total);
   return (int)cudaGetLastError();
 }

@@ -45,10 +45,11 @@ def _need_cuda(*ts: torch.Tensor) -> None:
                               f"(got device={t.device}, contiguous={t.is_contiguous()})")
 
 
-def embed(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor) -> None:
+def embed(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor, scale: float = 1.0) -> None:
+    """out[t] = table[tokens[t]] * scale, into the 32-bit residual stream."""
     _need_cuda(table, tokens, out)
     T, H = out.shape
-    check(library().mf_embed(table.data_ptr(), dtype_code(table), tokens.data_ptr(), out.data_ptr(), T, H,
+    check(library().mf_embed(table.data_ptr(), dtype_code(table), tokens.data_ptr(), out.data_ptr(), T, H, scale,
                              _stream()), "embed")
 
 
@@ -81,7 +82,7 @@ def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, seq_of_token: torc
                                      _stream()), "rope_kv_write")
 
 
-ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
+ACTIVATIONS = {"silu": 0, "gelu_tanh": 1, "relu2": 2}
 
 
 def activation_code(act: str) -> int:
@@ -97,6 +98,15 @@ def swiglu(gu: torch.Tensor, out: torch.Tensor, group: int, act: str = "silu") -
     T, I = out.shape
     check(library().mf_gated_act(gu.data_ptr(), out.data_ptr(), dtype_code(gu), T, I, group, activation_code(act),
                                  _stream()), "gated_act")
+
+
+def unary_act(x: torch.Tensor, out: torch.Tensor, act: str) -> None:
+    """out = act(x), element by element in 32-bit (``out`` may be ``x``)."""
+    _need_cuda(x, out)
+    if x.dtype != out.dtype or x.numel() != out.numel():
+        raise KernelError("unary_act: input and output of one dtype and size")
+    check(library().mf_unary_act(x.data_ptr(), out.data_ptr(), dtype_code(x), x.numel(), activation_code(act),
+                                 _stream()), "unary_act")
 
 
 def add_rmsnorm_pair(resid: torch.Tensor, d1: Optional[torch.Tensor], d2: Optional[torch.Tensor], w1: torch.Tensor,
@@ -194,39 +204,56 @@ def attention_decode_ex(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Ten
           "attention_decode_ex", launches=2)
 
 
-def latent_prepare(proj: torch.Tensor, q_rank: int, kv_off: int, rank: int, rot: int, wq: torch.Tensor,
+def latent_prepare(proj: torch.Tensor, q_rank: int, kv_off: int, rank: int, rot: int, wq: Optional[torch.Tensor],
                    wkv: Optional[torch.Tensor], eps: float, positions: torch.Tensor, seq_of_token: torch.Tensor,
-                   block_table: torch.Tensor, page_size: int, inv_f, inv_d, cq_out: torch.Tensor,
-                   k_pool: torch.Tensor, write_kv: bool) -> None:
+                   block_table: torch.Tensor, page_size: int, inv_f, inv_d, cq_out: Optional[torch.Tensor],
+                   k_pool: torch.Tensor, write_kv: bool, pairs: bool = False, rot_dims: Optional[int] = None,
+                   magnitude: float = 1.0) -> None:
     """From rows of projections [query latent | key/value latent, shared key part | ...]: the normed query
-    latent into ``cq_out`` and, if ``write_kv``, the normed latent and the rotated key part into the cache."""
+    latent into ``cq_out`` (``q_rank`` 0: there is none) and, if ``write_kv``, the normed latent and the rotated
+    key part into the cache.  ``pairs``: channel 2i turns with 2i+1, else i with i + rot_dims/2; ``rot_dims`` of
+    the ``rot`` channels turn (default all); cosine and sine are multiplied by ``magnitude``."""
     _need_cuda(proj, wq, wkv, cq_out, k_pool)
+    launches = 0 if (q_rank == 0 and not write_kv) else 1
     check(library().mf_latent_prepare(proj.data_ptr(), dtype_code(proj), proj.shape[0], proj.shape[1], q_rank, kv_off,
-                                      rank, rot, wq.data_ptr(), _ptr(wkv), eps, positions.data_ptr(),
+                                      rank, rot, _ptr(wq), _ptr(wkv), eps, positions.data_ptr(),
                                       seq_of_token.data_ptr(), block_table.data_ptr(), block_table.shape[1], page_size,
-                                      _ptr(inv_f), _ptr(inv_d), cq_out.data_ptr(), k_pool.data_ptr(), int(write_kv),
-                                      _stream()), "latent_prepare")
+                                      _ptr(inv_f), _ptr(inv_d), _ptr(cq_out), k_pool.data_ptr(), int(write_kv),
+                                      1 if pairs else 0, rot if rot_dims is None else rot_dims, magnitude,
+                                      _stream()), "latent_prepare", launches=launches)
 
 
 def latent_query(q: torch.Tensor, n_heads: int, dim: int, rot: int, rank: int, positions: torch.Tensor, inv_f, inv_d,
-                 q_full: torch.Tensor) -> None:
-    """The rotated part of every head's query, rotated, into columns [rank, rank + rot) of ``q_full``."""
-    _need_cuda(q, q_full)
-    check(library().mf_latent_query(q.data_ptr(), dtype_code(q), q.shape[0], n_heads, dim, rot, rank,
-                                    positions.data_ptr(), _ptr(inv_f), _ptr(inv_d), q_full.data_ptr(), _stream()),
+                 q_full: torch.Tensor, q_ld: Optional[int] = None, pairs: bool = False,
+                 rot_dims: Optional[int] = None, magnitude: float = 1.0) -> None:
+    """The rotated part of every head's query, rotated, into columns [rank, rank + rot) of ``q_full``; rows of
+    ``q`` are ``q_ld`` elements apart (default: as wide as their heads).  The rotation's options as in
+    ``latent_prepare``."""
+    _need_cuda(q_full)
+    if q_ld is None:
+        q_ld = n_heads * (dim + rot)
+    check(library().mf_latent_query(q.data_ptr(), q_ld, dtype_code(q), q.shape[0], n_heads, dim, rot, rank,
+                                    positions.data_ptr(), _ptr(inv_f), _ptr(inv_d), q_full.data_ptr(),
+                                    1 if pairs else 0, rot if rot_dims is None else rot_dims, magnitude, _stream()),
           "latent_query", launches=1 if rot else 0)
 
 
+def _gate_strides(N: int, gate_per_head: bool):
+    return (1, 0) if gate_per_head else (N, 1)
+
+
 def head_linear(x: torch.Tensor, x_ld: int, x_hs: int, w: torch.Tensor, out: torch.Tensor, out_ld: int, out_hs: int,
-                T: int, gate: Optional[torch.Tensor] = None, gate_ld: int = 0) -> None:
+                T: int, gate: Optional[torch.Tensor] = None, gate_ld: int = 0, gate_per_head: bool = False) -> None:
     """``out[t, h, :N] = w[h] @ x[t, h, :K]`` for ``w`` [heads, N, K]; rows of ``x`` / ``out`` are ``x_ld`` /
-    ``out_ld`` elements apart and heads ``x_hs`` / ``out_hs``; optionally times sigmoid(``gate[t, h * N + n]``)."""
+    ``out_ld`` elements apart and heads ``x_hs`` / ``out_hs``; optionally times sigmoid(``gate[t, h * N + n]``),
+    or, with ``gate_per_head``, sigmoid(``gate[t, h]``)."""
     _need_cuda(w)
     if x.dtype != w.dtype or out.dtype != w.dtype:
         raise KernelError("head_linear: operands of one dtype")
     H, N, K = w.shape
+    ghs, gns = _gate_strides(N, gate_per_head)
     check(library().mf_head_linear(x.data_ptr(), x_ld, x_hs, w.data_ptr(), out.data_ptr(), out_ld, out_hs,
-                                   dtype_code(w), T, H, N, K, _ptr(gate), gate_ld, _stream()), "head_linear")
+                                   dtype_code(w), T, H, N, K, _ptr(gate), gate_ld, ghs, gns, _stream()), "head_linear")
 
 
 def head_linear_mma_ok(x: torch.Tensor, x_ld: int, x_hs: int, w: torch.Tensor) -> bool:
@@ -236,12 +263,13 @@ def head_linear_mma_ok(x: torch.Tensor, x_ld: int, x_hs: int, w: torch.Tensor) -
 
 
 def head_linear_mma(x: torch.Tensor, x_ld: int, x_hs: int, w: torch.Tensor, out: torch.Tensor, out_ld: int, out_hs: int,
-                    T: int, gate: Optional[torch.Tensor] = None, gate_ld: int = 0) -> None:
+                    T: int, gate: Optional[torch.Tensor] = None, gate_ld: int = 0, gate_per_head: bool = False) -> None:
     """``head_linear`` for many bfloat16 tokens, on the tensor cores (mma.sync tiles of 64 tokens x 64 outputs)."""
     _need_cuda(w)
     H, N, K = w.shape
+    ghs, gns = _gate_strides(N, gate_per_head)
     check(library().mf_head_linear_mma(x.data_ptr(), x_ld, x_hs, w.data_ptr(), out.data_ptr(), out_ld, out_hs, T, H, N,
-                                       K, _ptr(gate), gate_ld, _stream()), "head_linear_mma")
+                                       K, _ptr(gate), gate_ld, ghs, gns, _stream()), "head_linear_mma")
 
 
 def retention_prepare(proj: torch.Tensor, n_heads: int, dim: int, rot: int, k_scale: float, positions: torch.Tensor,
@@ -371,6 +399,16 @@ def check_kernel_status() -> None:
         code = int(t.item())
         if code:
             raise kernel_gave_up(code, torch.device("cuda", key))
+
+
+def stream_linear_has_act() -> bool:
+    """Whether the few-row product has the activations without a gate in its epilogue."""
+    return False
+
+
+def gemm_has_act() -> bool:
+    """Whether the tcgen05 product has the activations without a gate in its epilogue."""
+    return False
 
 
 def stream_max_rows() -> int:
@@ -670,20 +708,28 @@ def delta_output(o: torch.Tensor, gate: torch.Tensor, gate_ld: int, weight: torc
 # ---------------------------------------------------------------------------- mixture of experts
 
 def moe_route(z: torch.Tensor, n_groups: int, keep: int, top: int, route_scale: float, ids: torch.Tensor,
-              weights: torch.Tensor) -> None:
-    _need_cuda(z, ids, weights)
-    check(library().mf_moe_route(z.data_ptr(), z.shape[0], z.shape[1], n_groups, keep, top, route_scale,
-                                 ids.data_ptr(), weights.data_ptr(), _stream()), "moe_route")
+              weights: torch.Tensor, n_experts: Optional[int] = None, softmax: bool = False,
+              bias: Optional[torch.Tensor] = None) -> None:
+    """The router's choice from logits ``z`` [T, >= n_experts] (the first ``n_experts`` columns of every row;
+    default all): scores by sigmoid or, with ``softmax``, by a softmax over the experts; ``bias`` (32-bit, one
+    per expert) is added for the choice only."""
+    _need_cuda(z, ids, weights, bias)
+    E = z.shape[1] if n_experts is None else n_experts
+    check(library().mf_moe_route(z.data_ptr(), z.shape[1], z.shape[0], E, n_groups, keep, top, route_scale,
+                                 1 if softmax else 0, _ptr(bias), ids.data_ptr(), weights.data_ptr(), _stream()),
+          "moe_route")
 
 
 def moe_rows(x: torch.Tensor, w_gu: torch.Tensor, w_down: torch.Tensor, ids: torch.Tensor, y: torch.Tensor,
-             limit: float, alpha: float) -> None:
+             limit: float, alpha: float, up_offset: float = 1.0) -> None:
     """y [T, top, moe_rows_slices(ff), H] (32-bit) = each chosen expert's output for its token, in the
-    partial sums of the slices its columns are cut into, not yet weighted."""
+    partial sums of the slices its columns are cut into, not yet weighted.  A choice beyond the stacked
+    experts (an identity expert) writes nothing."""
     _need_cuda(x, w_gu, w_down, ids, y)
     T, H = x.shape
     check(library().mf_moe_rows(x.data_ptr(), w_gu.data_ptr(), w_down.data_ptr(), dtype_code(x), ids.data_ptr(),
-                                y.data_ptr(), T, H, w_down.shape[2], ids.shape[1], limit, alpha, _stream()),
+                                y.data_ptr(), T, H, w_down.shape[2], ids.shape[1], limit, alpha, up_offset,
+                                w_down.shape[0], _stream()),
           "moe_rows")
 
 
@@ -693,11 +739,20 @@ def moe_rows_slices(ff: int) -> int:
 
 
 def moe_combine(y: torch.Tensor, weights: torch.Tensor, slot_of: Optional[torch.Tensor], out: torch.Tensor,
-                slices: int = 1) -> None:
-    _need_cuda(y, weights, slot_of, out)
+                slices: int = 1, ids: Optional[torch.Tensor] = None, n_real: int = 0,
+                x: Optional[torch.Tensor] = None, shared: Optional[torch.Tensor] = None,
+                shared_gate: Optional[torch.Tensor] = None, gate_ld: int = 0) -> None:
+    """The weighted sum of the chosen experts' outputs.  With ``ids``, ``n_real`` and ``x``: a choice from
+    ``n_real`` on is an identity expert and contributes ``x[t]``.  With ``shared`` [T, H]: it is added, times
+    sigmoid(``shared_gate[t * gate_ld]``) (32-bit logits, e.g. a column of the router's product) where given."""
+    _need_cuda(y, weights, slot_of, out, ids, x, shared)
     T, H = out.shape
+    for extra in (x, shared):
+        if extra is not None and extra.dtype != out.dtype:
+            raise KernelError("moe_combine: the input and the shared branch have the output's dtype")
     check(library().mf_moe_combine(y.data_ptr(), dtype_code(y), weights.data_ptr(), _ptr(slot_of), out.data_ptr(),
-                                   dtype_code(out), T, H, weights.shape[1], slices, _stream()), "moe_combine")
+                                   dtype_code(out), T, H, weights.shape[1], slices, _ptr(ids), n_real, _ptr(x),
+                                   _ptr(shared), _ptr(shared_gate), gate_ld, _stream()), "moe_combine")
 
 
 def attention_talking_tc_ok(n_heads: int, n_kv: int, dim: int, vdim: int, page_size: int) -> bool:
@@ -792,20 +847,22 @@ def moe_gather_rows(x: torch.Tensor, row_token: torch.Tensor, xg: torch.Tensor) 
                                        _stream()), "moe_gather_rows")
 
 
-def moe_activation(gu: torch.Tensor, act: torch.Tensor, limit: float, alpha: float) -> None:
+def moe_activation(gu: torch.Tensor, act: torch.Tensor, limit: float, alpha: float, up_offset: float = 1.0) -> None:
     """act [rows, ff] from a product gu [rows, 2 ff] (gate columns, then up columns): the clamped gated activation."""
     _need_cuda(gu, act)
     check(library().mf_moe_activation(gu.data_ptr(), act.data_ptr(), act.shape[0], act.shape[1], limit, alpha,
-                                      _stream()), "moe_activation")
+                                      up_offset, _stream()), "moe_activation")
 
 
 def moe_grouped_up(x: torch.Tensor, w_gu: torch.Tensor, row_token: torch.Tensor, meta: torch.Tensor,
-                   tiles: torch.Tensor, act: torch.Tensor, top: int, limit: float, alpha: float) -> None:
+                   tiles: torch.Tensor, act: torch.Tensor, top: int, limit: float, alpha: float,
+                   up_offset: float = 1.0) -> None:
     _need_cuda(x, w_gu, row_token, meta, tiles, act)
     T, H = x.shape
     E, _, ff, _ = w_gu.shape
     check(library().mf_moe_grouped_up(x.data_ptr(), w_gu.data_ptr(), row_token.data_ptr(), meta.data_ptr(),
-                                      tiles.data_ptr(), act.data_ptr(), T, H, ff, E, top, limit, alpha, _stream()),
+                                      tiles.data_ptr(), act.data_ptr(), T, H, ff, E, top, limit, alpha, up_offset,
+                                      _stream()),
           "moe_grouped_up")
 
 

@@ -111,15 +111,16 @@ class Runtime:
         return out
 
     def head_linear(self, x, x_ld: int, x_hs: int, w, out, out_ld: int, out_hs: int, T: int, gate=None,
-                    gate_ld: int = 0):
+                    gate_ld: int = 0, gate_per_head: bool = False):
         """A product per head: ``out[t, h, :] = w[h] @ x[t, h, :]`` for ``w`` [heads, N, K], rows and heads of
-        ``x`` and ``out`` at the given strides (in elements), optionally times ``sigmoid(gate[t, h * N + n])``;
+        ``x`` and ``out`` at the given strides (in elements), optionally times ``sigmoid(gate[t, h * N + n])``
+        (``gate_per_head``: ``sigmoid(gate[t, h])``, one number for all outputs of a head);
         32-bit accumulation, one rounding.  More than 16 bfloat16 tokens take the tensor-core kernel where the
         sizes allow it; few tokens and the 32-bit path the kernel with a warp per output."""
         if T > self.stream_max_rows and ops.head_linear_mma_ok(x, x_ld, x_hs, w):
-            ops.head_linear_mma(x, x_ld, x_hs, w, out, out_ld, out_hs, T, gate, gate_ld)
+            ops.head_linear_mma(x, x_ld, x_hs, w, out, out_ld, out_hs, T, gate, gate_ld, gate_per_head)
         else:
-            ops.head_linear(x, x_ld, x_hs, w, out, out_ld, out_hs, T, gate, gate_ld)
+            ops.head_linear(x, x_ld, x_hs, w, out, out_ld, out_hs, T, gate, gate_ld, gate_per_head)
         return out
 
     def _skinny(self, x, w) -> bool:
@@ -128,6 +129,23 @@ class Runtime:
     def _mid(self, x, w) -> bool:
         return ((self.mid_rows_enabled or self.gemm_backend == "tcgen05") and self.gemm_backend != "library"
                 and x.shape[0] <= self.mid_max_rows and ops.gemm_ok(x, w))
+
+    def linear_act(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, act: str) -> torch.Tensor:
+        """``out = act(x w^T)`` for an activation without a gate (``ops.ACTIVATIONS``), applied to the 32-bit
+        sums where the product's kernel has it in its epilogue (the few-row kernel and the tcgen05 one),
+        else to the rounded product by an elementwise kernel."""
+        if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
+            if self._skinny(x, w) and ops.stream_linear_has_act():
+                ops.stream_linear(x, w, out, act=act, unary=True)
+                return out
+            own = self.gemm_backend == "tcgen05" or (self.gemm_backend == "auto"
+                                                     and x.shape[0] >= self.fused_swiglu_min_rows)
+            if own and ops.gemm_ok(x, w) and ops.gemm_has_act():
+                ops.gemm_bf16(x, w, out, act=act, unary=True)
+                return out
+        self.linear(x, w, out)
+        ops.unary_act(out, out, act)
+        return out
 
     def linear_swiglu(self, x: torch.Tensor, w_gu: torch.Tensor, group: int, out: torch.Tensor,
                       act: str = "silu") -> torch.Tensor:

@@ -79,3 +79,24 @@ class ParallelBlock(Block):
         d1 = self.mixer.forward(x1, batch, cache, writes_cache)
         d2 = self.feed_forward.forward(x2, batch) if self.feed_forward is not None else None
         return residual, DeltaPair(d1, d2)
+
+
+@register_block("parallel_shared_norm")
+class ParallelSharedNormBlock(Block):
+    """Mixer and feed-forward side by side behind ONE norm: ``n = norm(h); h += mixer(n) + feed_forward(n)``.
+    Both branches read the same normalised rows.  The two deltas travel on as one ``DeltaPair`` that the
+    next layer's norm (or the final norm) adds in 32-bit in the kernel that normalises.  A layer without
+    a feed-forward has the mixer's branch only."""
+
+    roles = ("mixer", "mixer_norm")
+
+    def __init__(self, by_role, runtime):
+        super().__init__(by_role, runtime)
+        if self.feed_forward_norm is not None:
+            raise ValueError("parallel_shared_norm: the feed-forward reads the mixer's norm and has none of its own")
+
+    def forward(self, residual, pending, batch, cache, writes_cache: bool = True):
+        x = self.mixer_norm.add_forward(residual, pending)
+        d1 = self.mixer.forward(x, batch, cache, writes_cache)
+        d2 = self.feed_forward.forward(x, batch) if self.feed_forward is not None else None
+        return residual, DeltaPair(d1, d2)

@@ -1,4 +1,5 @@
-"""Token embedding (``h[t] = E[token[t]]``, src/model/decoder_model.cpp:194-204)
+"""Token embedding (``h[t] = E[token[t]]``, src/model/decoder_model.cpp:194-204;
+optionally times a constant ``scale``)
 into the 32-bit residual stream (into every stream, where a model has several;
 optionally plus a sinusoidal position vector), and the output head (``logits = hn W^T`` with
 ``W = lm_head.weight`` when the checkpoint has it, else the embedding table,
@@ -28,6 +29,11 @@ class TokenEmbedding(Part):
         if self.positions not in (None, "sinusoid"):
             raise ValueError(f"token_embedding: unknown positions '{self.positions}' (None or 'sinusoid')")
         self.theta = float(params.get("theta", 10000.0))
+        # the row is multiplied by this on its way into the residual stream (the head, where it shares
+        # the table, reads the table itself)
+        self.scale = float(params.get("scale", 1.0))
+        if self.scale != 1.0 and self.positions is not None:
+            raise ValueError("token_embedding: a scale together with added positions is not supported")
         self.freqs = None
         self.table = None
 
@@ -44,7 +50,7 @@ class TokenEmbedding(Part):
         return 0     # a step reads one row per token, not the table
 
     def forward(self, tokens, out):
-        ops.embed(self.table, tokens, out)
+        ops.embed(self.table, tokens, out, self.scale)
         return out
 
     def embed(self, batch, out, copies: int = 1):

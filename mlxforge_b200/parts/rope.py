@@ -19,6 +19,8 @@ before the rotation, for mixers whose values are their keys.
 """
 from __future__ import annotations
 
+import math
+
 import numpy as np
 import torch
 
@@ -95,6 +97,40 @@ def inverse_wavelengths(rotary_dim: int, base: float, device):
     i = np.arange(rotary_dim // 2, dtype=np.float64)
     inv = np.power(float(base), -2.0 * i / max(rotary_dim, 1))
     return (torch.from_numpy(inv.astype(np.float32)).to(device), torch.from_numpy(inv).to(device))
+
+
+def stretched_inverse_wavelengths(rotary_dim: int, base: float, scaling, device):
+    """Inverse wavelengths of a rotation whose slow pairs are stretched for contexts longer than the ones
+    trained on (the YaRN schedule), and the factor that goes with it on cosine and sine:
+    (float32 tensor, float64 tensor, factor).
+
+    ``scaling`` has ``factor``, ``original`` (the trained context), ``fast`` and ``slow`` (turns over that
+    context).  With ``w_i = base^(-2i/dims)`` and ``p(t) = dims ln(original / (2 pi t)) / (2 ln base)`` the
+    pair index at which a pair makes ``t`` turns over the trained context: pairs up to
+    ``lo = max(floor(p(fast)), 0)`` keep ``w_i``, pairs from ``hi = min(ceil(p(slow)), dims - 1)`` on get
+    ``w_i / factor``, and between them the two are blended linearly in the pair index (a ramp over
+    ``max(hi - lo, 0.001)``).  Cosine and sine are multiplied by ``0.1 ln(factor) + 1``.  ``scaling`` None:
+    the plain table and 1.  Worked out in double."""
+    if rotary_dim < 0 or rotary_dim % 2:
+        raise ValueError(f"rotary_dim must be even and not negative, got {rotary_dim}")
+    i = np.arange(rotary_dim // 2, dtype=np.float64)
+    inv = np.power(float(base), -2.0 * i / max(rotary_dim, 1))
+    magnitude = 1.0
+    if scaling:
+        factor, original = float(scaling["factor"]), float(scaling["original"])
+        fast, slow = float(scaling["fast"]), float(scaling["slow"])
+        if not (factor > 0 and original > 0 and fast > 0 and slow > 0 and base > 1):
+            raise ValueError("stretched rotation: factor, original, fast and slow must be positive, base above 1")
+
+        def pair_of(turns: float) -> float:
+            return rotary_dim * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(float(base)))
+
+        lo = max(math.floor(pair_of(fast)), 0)
+        hi = min(math.ceil(pair_of(slow)), rotary_dim - 1)
+        ramp = np.clip((i - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+        inv = inv / factor * ramp + inv * (1.0 - ramp)
+        magnitude = 0.1 * math.log(factor) + 1.0
+    return (torch.from_numpy(inv.astype(np.float32)).to(device), torch.from_numpy(inv).to(device), magnitude)
 
 
 @register_position("rotary")
