@@ -32,6 +32,8 @@ template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(flo
 #define MF_ACT_GELU_TANH 1      // 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))
 #define MF_ACT_RELU2 2          // max(z, 0)^2
 #define MF_ACT_COUNT 3
+// mode of a product whose epilogue applies activation a to every sum (no gate): MF_STREAM_UNARY + a
+#define MF_STREAM_UNARY 16
 __device__ __forceinline__ float gate_act(float g, int act) {
   if (act == MF_ACT_GELU_TANH) return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
   if (act == MF_ACT_RELU2) {

@@ -91,23 +91,29 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
 }
 template <int ACT> __device__ __forceinline__ float act_mul(float g, float u) { return gate_act(g, ACT) * u; }
 
+// a sum on its way into a bfloat16 C: as it is (EPI 0) or through the activation EPI - 4 (EPI >= 4)
+template <int EPI> __device__ __forceinline__ float epi_value(unsigned bits) {
+  const float v = __uint_as_float(bits);
+  return EPI >= 4 ? gate_act(v, EPI - 4) : v;
+}
+
 // Stores 32 consecutive columns of one row of the accumulator.
 template <int EPI>
 __device__ __forceinline__ void store_chunk(void* __restrict__ C, const unsigned (&r)[32], int row, int col, int N) {
-  if (EPI == 0) {
+  if (EPI == 0 || EPI >= 4) {
     __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(C) + (long long)row * N + col;
     if (col + 32 <= N && (((uintptr_t)dst) & 15) == 0) {
 #pragma unroll
       for (int v = 0; v < 4; v++) {
         uint4 pk;
-        pk.x = pack_bf16(__uint_as_float(r[8 * v + 0]), __uint_as_float(r[8 * v + 1]));
-        pk.y = pack_bf16(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3]));
-        pk.z = pack_bf16(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5]));
-        pk.w = pack_bf16(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7]));
+        pk.x = pack_bf16(epi_value<EPI>(r[8 * v + 0]), epi_value<EPI>(r[8 * v + 1]));
+        pk.y = pack_bf16(epi_value<EPI>(r[8 * v + 2]), epi_value<EPI>(r[8 * v + 3]));
+        pk.z = pack_bf16(epi_value<EPI>(r[8 * v + 4]), epi_value<EPI>(r[8 * v + 5]));
+        pk.w = pack_bf16(epi_value<EPI>(r[8 * v + 6]), epi_value<EPI>(r[8 * v + 7]));
         reinterpret_cast<uint4*>(dst)[v] = pk;
       }
     } else {
-      for (int j = 0; j < 32 && col + j < N; j++) dst[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
+      for (int j = 0; j < 32 && col + j < N; j++) dst[j] = __float2bfloat16_rn(epi_value<EPI>(r[j]));
     }
   } else if (EPI == 1) {
     float* dst = reinterpret_cast<float*>(C) + (long long)row * N + col;
@@ -142,6 +148,7 @@ __device__ __forceinline__ void store_chunk(void* __restrict__ C, const unsigned
 }
 
 // EPI 0: C bfloat16 [M, N].  EPI 1: C float32 [M, N].  EPI 2: C bfloat16 [M, N/2] = silu(gate) * up.
+// EPI 4 + a: C bfloat16 [M, N] = act_a(A W^T), no gate (a: MF_ACT_*).
 // Persistent: a block walks tiles (tile, tile + grid, ...; the M index runs fastest, so blocks
 // that run together share tiles of W).  Two accumulators in tensor memory alternate, so the
 // epilogue of one tile runs while the products of the next are issued.
@@ -276,7 +283,7 @@ int launch(const void* A, const void* W, void* C, int M, int N, int K, int* stat
   const int n_sms = mf_sm_count();
   if (n_sms <= 0) return MF_ERR_BAD_ARG;
   const int n_tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
-  mf_count(EPI >= 2 ? MF_K_GEMM_TC_SWIGLU : MF_K_GEMM_TC);
+  mf_count(EPI >= 4 ? MF_K_GEMM_TC_ACT : EPI >= 2 ? MF_K_GEMM_TC_SWIGLU : MF_K_GEMM_TC);
   gemm_kernel<BN, EPI><<<n_tiles < n_sms ? n_tiles : n_sms, 192, smem, stream>>>(ma, mw, C, M, N, K, status);
   return (int)cudaGetLastError();
 }
@@ -284,20 +291,24 @@ int launch(const void* A, const void* W, void* C, int M, int N, int K, int* stat
 }  // namespace
 
 // epilogue 0: C bfloat16 [M, N]; 1: C float32 [M, N]; 2 (SiLU), 3 (tanh-GELU): C bfloat16 [M, N/2] = act(gate) * up for a W
-// whose rows interleave gate and up in groups of 8 (N a multiple of 16).
+// whose rows interleave gate and up in groups of 8 (N a multiple of 16); 4 + a: C bfloat16 [M, N] = act_a(A W^T) for the
+// activation a (MF_ACT_*), applied to the 32-bit sums.
 // K must be a multiple of 8 and A, W 16-byte aligned (TMA strides).  `status` as in mf_stream_linear
 // (codes 11: producer, 12: MMA issuer, 13: epilogue).
 MF_API int mf_gemm_bf16(const void* A, const void* W, void* C, int M, int N, int K, int epilogue, int* status,
                         cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
-  if (K <= 0 || K % 8 || epilogue < 0 || epilogue > 3) return MF_ERR_BAD_ARG;
-  if (epilogue >= 2 && N % 16) return MF_ERR_BAD_ARG;
+  if (K <= 0 || K % 8 || epilogue < 0 || epilogue >= 4 + MF_ACT_COUNT) return MF_ERR_BAD_ARG;
+  if ((epilogue == 2 || epilogue == 3) && N % 16) return MF_ERR_BAD_ARG;
   if (((uintptr_t)A | (uintptr_t)W) & 15) return MF_ERR_BAD_ARG;
   const bool wide = N > 128;
   switch (epilogue) {
     case 0: return wide ? launch<256, 0>(A, W, C, M, N, K, status, stream) : launch<128, 0>(A, W, C, M, N, K, status, stream);
     case 1: return wide ? launch<256, 1>(A, W, C, M, N, K, status, stream) : launch<128, 1>(A, W, C, M, N, K, status, stream);
     case 2: return wide ? launch<256, 2>(A, W, C, M, N, K, status, stream) : launch<128, 2>(A, W, C, M, N, K, status, stream);
-    default: return wide ? launch<256, 3>(A, W, C, M, N, K, status, stream) : launch<128, 3>(A, W, C, M, N, K, status, stream);
+    case 3: return wide ? launch<256, 3>(A, W, C, M, N, K, status, stream) : launch<128, 3>(A, W, C, M, N, K, status, stream);
+    case 4: return wide ? launch<256, 4>(A, W, C, M, N, K, status, stream) : launch<128, 4>(A, W, C, M, N, K, status, stream);
+    case 5: return wide ? launch<256, 5>(A, W, C, M, N, K, status, stream) : launch<128, 5>(A, W, C, M, N, K, status, stream);
+    default: return wide ? launch<256, 6>(A, W, C, M, N, K, status, stream) : launch<128, 6>(A, W, C, M, N, K, status, stream);
   }
 }

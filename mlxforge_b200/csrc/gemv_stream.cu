@@ -192,13 +192,14 @@ stream_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restri
       }
     }
     consumer_sync();
-    if (mode == 0) {
+    if (mode == 0 || mode >= MF_STREAM_UNARY) {
       for (int i = threadIdx.x; i < ROWS * NB * 8; i += CW * 32) {
         const int m = i / ROWS, r = i - m * ROWS;
         if (m >= M || n0 + r >= N) continue;
         float sum = 0.f;
 #pragma unroll
         for (int w = 0; w < CW; w++) sum += red[(w * ROWS + r) * RED_M + m];
+        if (mode >= MF_STREAM_UNARY) sum = gate_act(sum, mode - MF_STREAM_UNARY);
         out[(long long)m * N + n0 + r] = from_f32<OutT>(sum);
       }
     } else {
@@ -340,13 +341,14 @@ stream_tmap_kernel(const __nv_bfloat16* __restrict__ x, const __grid_constant__ 
       }
     }
     consumer_sync();
-    if (mode == 0) {
+    if (mode == 0 || mode >= MF_STREAM_UNARY) {
       for (int i = threadIdx.x; i < ROWS * NB * 8; i += CW * 32) {
         const int m = i / ROWS, r = i - m * ROWS;
         if (m >= M || n0 + r >= N) continue;
         float sum = 0.f;
 #pragma unroll
         for (int w = 0; w < CW; w++) sum += red[(w * ROWS + r) * RED_M + m];
+        if (mode >= MF_STREAM_UNARY) sum = gate_act(sum, mode - MF_STREAM_UNARY);
         out[(long long)m * N + n0 + r] = from_f32<OutT>(sum);
       }
     } else {
@@ -421,7 +423,7 @@ int dispatch(const __nv_bfloat16* x, const __nv_bfloat16* W, OutT* out, int M, i
   const int n_sms = mf_sm_count();
   if (n_sms <= 0) return MF_ERR_BAD_ARG;
   // few output rows: tiles of 8 rows, so that there are blocks for every SM
-  const bool small = mode == 0 && (N + 15) / 16 < 2 * n_sms;
+  const bool small = (mode == 0 || mode >= MF_STREAM_UNARY) && (N + 15) / 16 < 2 * n_sms;
   // Tensor copies for every width of whole 64-column spans; a box that hangs over the end of the
   // matrix along K arrives with zeros there and counts its full size.  (Widths that are not whole
   // stages were once kept off this path because 3 x 128256 x 64 gave wrong rows: that was the
@@ -461,14 +463,16 @@ MF_API int mf_set_stream_tensor_copies(int on) {
 }
 
 // mode 0: out [M, N] in out_dtype.  mode 1 (SiLU) and 2 (tanh form of GELU): W rows interleave gate and up in groups of 8 (N a
-// multiple of 16) and out is [M, N / 2] = act(gate) * up.  K must be a multiple of 8 and x, W
+// multiple of 16) and out is [M, N / 2] = act(gate) * up.  mode MF_STREAM_UNARY + a: out [M, N] = act_a(x W^T), the
+// activation (MF_ACT_*) applied to the 32-bit sums before they are rounded.  K must be a multiple of 8 and x, W
 // 16-byte aligned.  `status`: a device int (may be null) that receives a non-zero code if a wait
 // inside the kernel ran out (1: producer, 2: consumer).
 MF_API int mf_stream_linear(const void* x, const void* W, void* out, int out_dtype, int M, int N, int K, int mode,
                             int* status, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
-  if (K <= 0 || K % 8 || M > 16 || mode < 0 || mode > 2) return MF_ERR_BAD_ARG;
-  if (mode != 0 && N % 16) return MF_ERR_BAD_ARG;
+  const bool unary = mode >= MF_STREAM_UNARY && mode < MF_STREAM_UNARY + MF_ACT_COUNT;
+  if (K <= 0 || K % 8 || M > 16 || mode < 0 || (mode > 2 && !unary)) return MF_ERR_BAD_ARG;
+  if (mode != 0 && !unary && N % 16) return MF_ERR_BAD_ARG;
   if (((uintptr_t)x | (uintptr_t)W) & 15) return MF_ERR_BAD_ARG;
   const __nv_bfloat16 *xx = (const __nv_bfloat16*)x, *ww = (const __nv_bfloat16*)W;
   if (out_dtype == MF_BF16) return dispatch<__nv_bfloat16>(xx, ww, (__nv_bfloat16*)out, M, N, K, mode, status, stream);

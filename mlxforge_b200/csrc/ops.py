@@ -83,6 +83,7 @@ def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, seq_of_token: torc
 
 
 ACTIVATIONS = {"silu": 0, "gelu_tanh": 1, "relu2": 2}
+STREAM_UNARY = 16      # mode of the few-row product with an activation without a gate: STREAM_UNARY + code
 
 
 def activation_code(act: str) -> int:
@@ -403,12 +404,12 @@ def check_kernel_status() -> None:
 
 def stream_linear_has_act() -> bool:
     """Whether the few-row product has the activations without a gate in its epilogue."""
-    return False
+    return True
 
 
 def gemm_has_act() -> bool:
     """Whether the tcgen05 product has the activations without a gate in its epilogue."""
-    return False
+    return True
 
 
 def stream_max_rows() -> int:
@@ -422,10 +423,11 @@ def set_stream_tensor_copies(on: bool) -> None:
 
 
 def stream_linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swiglu: bool = False,
-                  act: str = "silu") -> None:
+                  act: str = "silu", unary: bool = False) -> None:
     """out = x @ w^T for at most ``stream_max_rows()`` rows of bfloat16 x (out bfloat16 or
     float32), the weights streamed by bulk copies (see gemv_stream.cu); with ``swiglu`` the rows
-    of w interleave gate and up in groups of 8 and out [M, N/2] is silu(gate) * up.
+    of w interleave gate and up in groups of 8 and out [M, N/2] is act(gate) * up; with ``unary``
+    out [M, N] is act(x @ w^T), the activation applied to the 32-bit sums.
     The kernel starts fetching ``w`` before it waits for the kernel launched before it, so
     ``w`` must not be the output of that kernel (the engine's weights are written once, at
     load time)."""
@@ -435,9 +437,11 @@ def stream_linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swiglu: b
     want = (M, N // 2) if swiglu else (M, N)
     if w.shape[1] != K or tuple(out.shape) != want:
         raise KernelError(f"stream_linear: shapes {tuple(x.shape)} x {tuple(w.shape)}^T -> {tuple(out.shape)}")
+    if swiglu and unary:
+        raise KernelError("stream_linear: an activation with a gate or without one, not both")
+    mode = 1 + activation_code(act) if swiglu else (STREAM_UNARY + activation_code(act) if unary else 0)
     check(library().mf_stream_linear(x.data_ptr(), w.data_ptr(), out.data_ptr(), dtype_code(out), M, N, K,
-                                     1 + activation_code(act) if swiglu else 0, kernel_status(x.device).data_ptr(),
-                                     _stream()),
+                                     mode, kernel_status(x.device).data_ptr(), _stream()),
           "stream_linear")
 
 
@@ -476,19 +480,26 @@ def gemm_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
             and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
-def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swiglu: bool = False, act: str = "silu") -> None:
+def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swiglu: bool = False, act: str = "silu",
+              unary: bool = False) -> None:
     """out = x @ w^T on the tcgen05 tensor cores (bfloat16 operands; out bfloat16 or float32);
     with ``swiglu`` the rows of w interleave gate and up in groups of 8 and out is
-    [M, N/2] = silu(gate) * up."""
+    [M, N/2] = act(gate) * up; with ``unary`` out [M, N] (bfloat16) is act(x @ w^T), the activation
+    applied to the 32-bit sums."""
     _need_cuda(x, w, out)
     M, K = x.shape
     N = w.shape[0]
     want = (M, N // 2) if swiglu else (M, N)
     if w.shape[1] != K or tuple(out.shape) != want:
         raise KernelError(f"gemm_bf16: shapes {tuple(x.shape)} x {tuple(w.shape)}^T -> {tuple(out.shape)}")
-    if swiglu and out.dtype != torch.bfloat16:
-        raise KernelError("gemm_bf16: the gated epilogue writes bfloat16")
-    epi = 2 + activation_code(act) if swiglu else (1 if out.dtype == torch.float32 else 0)
+    if (swiglu or unary) and out.dtype != torch.bfloat16:
+        raise KernelError("gemm_bf16: an epilogue with an activation writes bfloat16")
+    if swiglu and unary:
+        raise KernelError("gemm_bf16: an activation with a gate or without one, not both")
+    if swiglu and act == "relu2":
+        raise KernelError("gemm_bf16: the gated epilogue has SiLU and the tanh form of GELU")
+    epi = (2 + activation_code(act) if swiglu else 4 + activation_code(act) if unary
+           else (1 if out.dtype == torch.float32 else 0))
     check(library().mf_gemm_bf16(x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, epi,
                                  kernel_status(x.device).data_ptr(), _stream()), "gemm_bf16")
 

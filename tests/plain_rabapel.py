@@ -144,6 +144,16 @@ def route_softmax(h, router, correction, top):
     return order, np.take_along_axis(s, order, axis=-1)
 
 
+def choice_margin(h, router, correction, top):
+    """[T]: how far the last chosen expert's choice score lies above the first one left out (infinite when
+    every output is chosen).  A small margin is a close call that rounding may turn the other way."""
+    z = h @ router.T
+    s = np.exp(z - z.max(axis=-1, keepdims=True))
+    s = s / s.sum(axis=-1, keepdims=True)
+    c = -np.sort(-(s if correction is None else s + correction), axis=-1)
+    return c[:, top - 1] - c[:, top] if c.shape[1] > top else np.full(h.shape[0], np.inf)
+
+
 def mixture_ff(h, w, mlp):
     """``w``: the feed-forward's tensors (``router, correction, e<i>.gate|up|down, shared.gate|up|down|sg``);
     ``mlp``: its configuration.  The router has ``experts + identity`` outputs; the last ``identity`` of
@@ -168,9 +178,10 @@ def _sub(tensors, prefix):
     return {k[len(prefix):]: v for k, v in tensors.items() if k.startswith(prefix)}
 
 
-def forward(cfg, tensors, tokens, layers_out=None):
+def forward(cfg, tensors, tokens, layers_out=None, margins_out=None):
     """Logits [T, vocab] of one whole sequence.  ``tensors``: name -> float64 array.  ``layers_out``: a
-    list that receives the residual stream after every layer."""
+    list that receives the residual stream after every layer; ``margins_out``: a list that receives every
+    mixture layer's ``choice_margin`` [T]."""
     eps = float(cfg["norm"]["eps"])
     x = tensors["embed"][np.asarray(tokens)] * float((cfg.get("embedding") or {}).get("scale", 1.0))
     for i, layer in enumerate(cfg["layers"]):
@@ -180,6 +191,8 @@ def forward(cfg, tensors, tokens, layers_out=None):
         mlp = layer.get("mlp")
         if mlp is not None:
             w = _sub(tensors, p + "mlp.")
+            if margins_out is not None and mlp["kind"] != "dense":
+                margins_out.append(choice_margin(h, w["router"], w.get("correction"), int(mlp["router"]["top"])))
             delta = delta + _r(relu2_ff(h, w) if mlp["kind"] == "dense" else mixture_ff(h, w, mlp))
         x = x + delta
         if layers_out is not None:
