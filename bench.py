@@ -476,6 +476,11 @@ def kernel_work(name, a, k, info):
     if name == "_grouped_mm":
         x, w = a[0], a[1]
         return (0, 2.0 * x.shape[0] * w.shape[1] * w.shape[2], 0)
+    if name in ("moe_route", "moe_sort", "unary_act"):
+        return (_nbytes(*[t for t in a if hasattr(t, "numel")]), 0, 0)
+    if name == "mid_linear":
+        x, w, out = a[0], a[1], a[2]
+        return (_nbytes(x, w, out), 2.0 * x.shape[0] * w.shape[0] * w.shape[1], 0)
     if name in ("moe_gather_rows", "moe_activation"):
         return (_nbytes(*[t for t in a if hasattr(t, "numel") and t.dim() >= 2]), 0, 0)
     if name == "moe_rows":
@@ -701,6 +706,93 @@ def run_luzinex(args) -> int:
     return 0
 
 
+# ---------------------------------------------------------------------------- --workload rabapel
+# The Rabapel design at sizes that resemble a real model's layers, beside the closest existing model at
+# equal size: a Luzinex decoder made of latent-attention layers only (the same width, layers, vocabulary,
+# heads, head sizes and latent rank; its queries through a latent of their own, no window, a gate per
+# channel), with gated feed-forwards of the dense layers' parameter count.  Rabapel's layers alternate a
+# dense squared-rectifier feed-forward and a mixture with identity experts and a gated shared expert; the
+# mixture's kernels are those of the Notirax design (--workload notirax lists them at its sizes).
+RABAPEL_SIZES = {
+    "s": dict(width=1024, layers=6, vocab=32768, ff=4096, heads=8, dim=64, rot=32, vdim=64, kv_rank=128, q_rank=384,
+              window=1024, experts=16, identity=2, top=4, expert_ff=512, shared_ff=1024, context=4096),
+    "m": dict(width=2048, layers=6, vocab=32768, ff=8192, heads=16, dim=64, rot=32, vdim=64, kv_rank=192, q_rank=768,
+              window=2048, experts=32, identity=4, top=6, expert_ff=768, shared_ff=2048, context=4096),
+}
+RABAPEL_KERNELS = ("embed", "add_rmsnorm_pair", "latent_prepare", "latent_query", "head_linear", "head_linear_mma",
+                   "attention_prefill_ex", "attention_decode_ex", "attention_generic_ex", "moe_route", "moe_rows",
+                   "moe_combine", "moe_sort", "moe_grouped_up", "moe_grouped_down", "moe_gather_rows", "moe_activation",
+                   "_grouped_mm", "swiglu", "unary_act", "mid_linear", "stream_linear", "gemm_bf16")
+
+
+def rabapel_config(z):
+    mixer = {"heads": z["heads"], "dim": z["dim"], "rot_dim": z["rot"], "vdim": z["vdim"], "kv_rank": z["kv_rank"],
+             "scale": (z["dim"] + z["rot"]) ** -0.5, "mask": {"size": z["window"]},
+             "rot": {"base": 500000.0, "dims": z["rot"],
+                     "scaling": {"factor": 8.0, "original": z["context"] // 8, "fast": 32.0, "slow": 1.0}}}
+    dense = {"kind": "dense", "ff": z["ff"]}
+    moe = {"kind": "moe", "expert": {"ff": z["expert_ff"]}, "shared": {"ff": z["shared_ff"]},
+           "router": {"experts": z["experts"], "identity": z["identity"], "top": z["top"]}}
+    return {"architecture": "Rabapel", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-6},
+            "embedding": {"scale": 0.5},
+            "layers": [{"type": "latent_attention", "mixer": dict(mixer), "mlp": dense if i % 2 == 0 else moe}
+                       for i in range(z["layers"])]}
+
+
+def rabapel_luzinex_like(z):
+    latent = {"heads": z["heads"], "dim": z["dim"], "rot_dim": z["rot"], "vdim": z["vdim"], "q_rank": z["q_rank"],
+              "kv_rank": z["kv_rank"], "scale": (z["dim"] + z["rot"]) ** -0.5, "rot": {"base": 500000.0, "dims": z["rot"]}}
+    # a gated feed-forward has three matrices where the squared-rectifier one has two
+    mlp = {"kind": "dense", "ff": z["ff"] * 2 // 3 // 128 * 128}
+    return {"architecture": "Luzinex", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-5},
+            "layers": [{"type": "latent_attention", "mixer": dict(latent), "mlp": mlp} for _ in range(z["layers"])]}
+
+
+def run_rabapel(args) -> int:
+    import torch
+    import mlxforge_b200 as mf
+    from mlxforge_b200.config import config_from_json
+    from mlxforge_b200.csrc import ops
+    pk = peaks()
+    out = {"workload": "rabapel", "dtype": "bf16", "peaks": pk,
+           "data": "synthetic: seeded random weights, seeded uniform token ids, random cache contents",
+           "fp32_tflops_nominal": round(FP32_TFLOPS_NOMINAL, 1), "sizes": {}}
+    clocks = ClockSampler()
+    clocks.start()
+    for key in ([args.size] if args.size else sorted(RABAPEL_SIZES)):
+        z = RABAPEL_SIZES[key]
+        res = {"size": z}
+        for which, cfg_json, names in (("rabapel", rabapel_config(z), RABAPEL_KERNELS),
+                                       ("luzinex_latent_equal_size", rabapel_luzinex_like(z), LUZINEX_KERNELS)):
+            tmp = tempfile.mkdtemp(prefix="mlxforge_bench_")
+            try:
+                d = mf.write_random_model(os.path.join(tmp, "model"), config_from_json(cfg_json), seed=0, dtype="bfloat16")
+                engine = mf.Engine(model_spec=d, dtype="bfloat16", kv_pool_tokens=(args.batch + 2) * (z["context"] + 2048 + 64),
+                                   max_running=max(8, args.batch), token_budget=8192, prefill_chunk=2048)
+            finally:
+                shutil.rmtree(tmp, ignore_errors=True)
+            for pool in set(engine.cache._k + engine.cache._v):
+                pool.normal_(0.0, 1.0)
+            ctx = z["context"]
+            t_pre = prefill_device(engine, PREFILL_TOKENS, runs=3, warmup=3)
+            sec, launches, _, _ = decode_device(engine, args.batch, ctx, args.steps, args.warmup)
+            r = {"prefill_tokens": PREFILL_TOKENS, "prefill_ms": round(t_pre * 1e3, 3),
+                 "prefill_tokens_per_s": round(PREFILL_TOKENS / t_pre, 1), "decode_batch": args.batch, "decode_context": ctx,
+                 "decode_ms_per_step": round(sec * 1e3, 4), "decode_tokens_per_s": round(args.batch / sec, 1),
+                 "decode_launches_per_step": launches, "graph_replays": engine.runner.graph_replays,
+                 "weight_bytes_per_step": engine.model.weight_bytes()}
+            if not args.skip_points:
+                r["kernels"] = kernel_table(engine, names, PREFILL_TOKENS, args.batch, ctx, 0, pk, extra={"ctx": ctx})
+            ops.check_kernel_status()
+            res[which] = r
+            del engine
+            torch.cuda.empty_cache()
+        out["sizes"][key] = res
+    out["clocks"] = clocks.stop()
+    print(json.dumps(out))
+    return 0
+
+
 # Kinds of launches that `--without` leaves out of a decode step, to see what each costs inside it.
 LEFT_OUT = ("norms", "rotation", "attention", "qkv", "o", "gate_up", "down", "head", "products")
 
@@ -755,11 +847,12 @@ def main() -> int:
     ap.add_argument("--without", default=None, choices=sorted(LEFT_OUT),
                     help="with --only decode: time the step with the launches of one kind left out (its results are "
                          "wrong; the difference to the full step is what that kind costs inside the step)")
-    ap.add_argument("--workload", default="headline", choices=["headline", "serving", "longctx", "notirax", "luzinex"],
+    ap.add_argument("--workload", default="headline", choices=["headline", "serving", "longctx", "notirax", "luzinex", "rabapel"],
                     help="serving: 64 requests on the 3B shape; longctx: 8 x 16,384 tokens on the 8B shape; notirax / "
-                         "luzinex: prefill and decode of that design beside the Llama decoder at equal size, per kernel")
-    ap.add_argument("--size", default=None, choices=sorted(set(NOTIRAX_SIZES) | set(LUZINEX_SIZES)),
-                    help="with --workload notirax or luzinex: one size only")
+                         "luzinex: prefill and decode of that design beside the Llama decoder at equal size, per kernel; "
+                         "rabapel: the same beside a Luzinex decoder of latent-attention layers at equal size")
+    ap.add_argument("--size", default=None, choices=sorted(set(NOTIRAX_SIZES) | set(LUZINEX_SIZES) | set(RABAPEL_SIZES)),
+                    help="with --workload notirax, luzinex or rabapel: one size only")
     args = ap.parse_args()
     args.shape_given = args.shape is not None
     args.shape = args.shape or "1b"
@@ -775,6 +868,8 @@ def main() -> int:
         return run_notirax(args)
     if args.workload == "luzinex":
         return run_luzinex(args)
+    if args.workload == "rabapel":
+        return run_rabapel(args)
     if args.workload != "headline":
         return run_workload(args)
 
