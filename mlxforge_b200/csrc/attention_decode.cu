@@ -59,7 +59,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
                    const __nv_bfloat16* __restrict__ v_pool, float* __restrict__ part_o,
                    float* __restrict__ part_ml, const int* __restrict__ positions,
                    const int* __restrict__ seq_of_token, PagedView pv, int n_heads, float scale_log2,
-                   int window, int max_splits, AttnOptions opt) {
+                   int window, int max_splits, int split_keys, AttnOptions opt) {
   constexpr int KPW = Tile<HD_MAX>::KPW;
   constexpr int WARPS = Tile<HD_MAX>::W;
   constexpr int TILE = KPW * WARPS;
@@ -84,13 +84,13 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
   const int n_rows = min(16, G - hg * 16);
   const int pos = positions[t], seq = seq_of_token[t];
   const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
-  const int k_begin = split * SPLIT_KEYS;
+  const int k_begin = split * split_keys;
   // keys below `keep` stay visible before the window (a split that holds some walks from its start)
   const int keep = (window > 0 && opt.keep_first > 0) ? min(opt.keep_first, lo) : 0;
-  if (k_begin > pos || (k_begin + SPLIT_KEYS <= lo && k_begin >= keep)) return;   // nothing visible in this split
+  if (k_begin > pos || (k_begin + split_keys <= lo && k_begin >= keep)) return;   // nothing visible in this split
   // tiles of this split that hold visible keys
   const int tile0 = (k_begin < keep ? k_begin : max(k_begin, lo)) / TILE;
-  const int tile1 = min(k_begin + SPLIT_KEYS - 1, pos) / TILE;
+  const int tile1 = min(k_begin + split_keys - 1, pos) / TILE;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int chunks = hd >> 3;            // 16-byte pieces per row
@@ -353,10 +353,9 @@ template <int HD_MAX>
 int launch_decode(const __nv_bfloat16* q, const __nv_bfloat16* k_pool, const __nv_bfloat16* v_pool,
                   __nv_bfloat16* out, float* part_o, float* part_ml, int n_tokens, int n_heads, PagedView pv,
                   const int* positions, const int* seq_of_token, float scale, int window, int max_ctx,
-                  AttnOptions opt, cudaStream_t stream) {
+                  AttnOptions opt, int SPLIT, cudaStream_t stream) {
   constexpr int KPW = Tile<HD_MAX>::KPW;
   constexpr int WARPS = Tile<HD_MAX>::W;
-  constexpr int SPLIT = SPLIT_KEYS;
   const int hd = pv.head_dim, ld = hd + 8;
   const int max_splits = (max_ctx + SPLIT - 1) / SPLIT;
   const int G = n_heads / pv.n_kv_heads;
@@ -380,7 +379,7 @@ int launch_decode(const __nv_bfloat16* q, const __nv_bfloat16* k_pool, const __n
   mf_count(MF_K_ATTN_DECODE_MERGE);
   cudaError_t e = launch_dep(attn_decode_kernel<HD_MAX>, grid, dim3(WARPS * 32), smem, stream, q, k_pool, v_pool,
                              part_o, part_ml, positions, seq_of_token, pv, n_heads, scale * LOG2E, window, max_splits,
-                             opt);
+                             SPLIT, opt);
   if (e != cudaSuccess) return (int)e;
   dim3 mgrid(n_tokens, n_heads);
   const int vd = opt.vd > 0 ? opt.vd : hd;
@@ -434,6 +433,16 @@ MF_API int mf_attention_decode_split(int hd) {
   return SPLIT_KEYS;
 }
 
+// Keys per split of the launch with options.  A window of a few thousand keys leaves a token only
+// window / split + 1 splits with keys in them, so few sequences would fill few blocks with long walks:
+// such lanes take short splits (more blocks, each two tiles long).  It depends on the lane's sizes only,
+// so a token's result does not depend on what else is in the batch.
+constexpr int WINDOW_SPLIT_KEYS = 128, SHORT_SPLIT_MAX_WINDOW = 4096;
+MF_API int mf_attention_decode_ex_split(int hd, int window) {
+  (void)hd;
+  return window > 0 && window <= SHORT_SPLIT_MAX_WINDOW ? WINDOW_SPLIT_KEYS : SPLIT_KEYS;
+}
+
 // Scratch: part_o  [n_tokens * n_heads * max_splits * hd] floats,
 //          part_ml [n_tokens * n_heads * max_splits * 2] floats, max_splits = ceil(max_ctx / split).
 // `max_ctx` bounds position + 1 of every token; a larger value only costs idle blocks.
@@ -476,17 +485,18 @@ MF_API int mf_attention_decode_hinted(const void* q, const void* k_pool, const v
   }
   if (hd <= 64)
     return launch_decode<64>(qq, kk, vv, oo, part_o, part_ml, n_tokens, n_heads, pv, positions, seq_of_token, scale,
-                             window, max_ctx, AttnOptions{}, stream);
+                             window, max_ctx, AttnOptions{}, SPLIT_KEYS, stream);
   if (hd <= 128)
     return launch_decode<128>(qq, kk, vv, oo, part_o, part_ml, n_tokens, n_heads, pv, positions, seq_of_token,
-                              scale, window, max_ctx, AttnOptions{}, stream);
+                              scale, window, max_ctx, AttnOptions{}, SPLIT_KEYS, stream);
   return launch_decode<256>(qq, kk, vv, oo, part_o, part_ml, n_tokens, n_heads, pv, positions, seq_of_token, scale,
-                            window, max_ctx, AttnOptions{}, stream);
+                            window, max_ctx, AttnOptions{}, SPLIT_KEYS, stream);
 }
 
 // The same with the options of AttnOptions (value width, values inside the keys, kept first keys, sink,
 // output gate), always on the kernel without tensor copies and with the merge kernel after it.  `out`
-// and the gate are [n_tokens, n_heads * vd]; the scratch is sized as for mf_attention_decode.
+// and the gate are [n_tokens, n_heads * vd]; the scratch is sized as for mf_attention_decode, with the
+// split that mf_attention_decode_ex_split gives.
 MF_API int mf_attention_decode_ex(const void* q, const void* k_pool, const void* v_pool, void* out, float* part_o,
                                   float* part_ml, int n_tokens, int n_heads, int n_kv, int hd, const int* positions,
                                   const int* seq_of_token, const int* block_table, int bt_stride, int page_size,
@@ -500,14 +510,15 @@ MF_API int mf_attention_decode_ex(const void* q, const void* k_pool, const void*
   const __nv_bfloat16 *qq = (const __nv_bfloat16*)q, *kk = (const __nv_bfloat16*)k_pool,
                       *vv = (const __nv_bfloat16*)v_pool;
   __nv_bfloat16* oo = (__nv_bfloat16*)out;
+  const int split = mf_attention_decode_ex_split(hd, window);
   if (hd <= 64)
     return launch_decode<64>(qq, kk, vv, oo, part_o, part_ml, n_tokens, n_heads, pv, positions, seq_of_token, scale,
-                             window, max_ctx, opt, stream);
+                             window, max_ctx, opt, split, stream);
   if (hd <= 128)
     return launch_decode<128>(qq, kk, vv, oo, part_o, part_ml, n_tokens, n_heads, pv, positions, seq_of_token,
-                              scale, window, max_ctx, opt, stream);
+                              scale, window, max_ctx, opt, split, stream);
   return launch_decode<256>(qq, kk, vv, oo, part_o, part_ml, n_tokens, n_heads, pv, positions, seq_of_token, scale,
-                            window, max_ctx, opt, stream);
+                            window, max_ctx, opt, split, stream);
 }
 
 MF_API int mf_attention_decode(const void* q, const void* k_pool, const void* v_pool, void* out, float* part_o,

@@ -41,6 +41,7 @@ _SIGNATURES = {
                              c_int, c_float, c_int, _P, _P],
     "mf_set_prefill_tcgen05": [c_int],
     "mf_attention_decode_split": [c_int],
+    "mf_attention_decode_ex_split": [c_int, c_int],
     "mf_attention_decode": [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, _P, _P, _P, c_int, c_int,
                             c_float, c_int, c_int, _P],
     "mf_attention_decode_hinted": [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, _P, _P, _P, c_int, c_int,

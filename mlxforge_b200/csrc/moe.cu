@@ -317,26 +317,47 @@ moe_combine_kernel(const TY* __restrict__ y, const float* __restrict__ weights, 
   }
 }
 
-// bfloat16 rows in 16-byte pieces (H a multiple of 8, one partial sum per pair): 8 columns a thread
+// bfloat16 rows in 16-byte pieces (H a multiple of 8, one partial sum per pair): 8 columns a thread;
+// identity experts and the shared branch as in the kernel above
 __global__ void __launch_bounds__(256)
 moe_combine_bf16_vec_kernel(const __nv_bfloat16* __restrict__ y, const float* __restrict__ weights,
-                            const int* __restrict__ slot_of, __nv_bfloat16* __restrict__ out, int H, int top) {
+                            const int* __restrict__ slot_of, __nv_bfloat16* __restrict__ out, int H, int top,
+                            MoeExtras ex) {
   pdl_launch();
   pdl_wait();
   const int t = blockIdx.x;
   const int i = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
   if (i >= H) return;
+  const __nv_bfloat16* x = reinterpret_cast<const __nv_bfloat16*>(ex.x);
+  const __nv_bfloat16* shared = reinterpret_cast<const __nv_bfloat16*>(ex.shared);
   float a[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
   for (int k = 0; k < top; k++) {
-    const long long row = slot_of ? slot_of[(long long)t * top + k] : (long long)t * top + k;
     const float wk = weights[(long long)t * top + k];
-    const uint4 v = *reinterpret_cast<const uint4*>(y + row * H + i);
+    const __nv_bfloat16* src;
+    if (ex.ids && ex.ids[(long long)t * top + k] >= ex.n_real) {
+      src = x + (long long)t * H + i;              // an identity expert returns the token's input
+    } else {
+      const long long row = slot_of ? slot_of[(long long)t * top + k] : (long long)t * top + k;
+      src = y + row * H + i;
+    }
+    const uint4 v = *reinterpret_cast<const uint4*>(src);
     const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
 #pragma unroll
     for (int j = 0; j < 4; j++) {
       const float2 f = __bfloat1622float2(p[j]);
       a[2 * j] = fmaf(wk, f.x, a[2 * j]);
       a[2 * j + 1] = fmaf(wk, f.y, a[2 * j + 1]);
+    }
+  }
+  if (shared) {
+    const float sg = ex.shared_gate ? moe_sigmoid(ex.shared_gate[(long long)t * ex.gate_ld]) : 1.0f;
+    const uint4 v = *reinterpret_cast<const uint4*>(shared + (long long)t * H + i);
+    const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      const float2 f = __bfloat1622float2(p[j]);
+      a[2 * j] = fmaf(sg, f.x, a[2 * j]);
+      a[2 * j + 1] = fmaf(sg, f.y, a[2 * j + 1]);
     }
   }
   uint4 o;
@@ -353,10 +374,10 @@ MF_API int mf_moe_combine(const void* y, int y_dtype, const float* weights, cons
   if (ids && !x) return MF_ERR_BAD_ARG;
   const MoeExtras ex{ids, n_real, x, shared, shared_gate, gate_ld};
   mf_count(MF_K_MOE_COMBINE);
-  if (!ids && !shared && y_dtype == MF_BF16 && out_dtype == MF_BF16 && slices == 1 && H % 8 == 0 && ((uintptr_t)y & 15) == 0 &&
-      ((uintptr_t)out & 15) == 0)
+  if (y_dtype == MF_BF16 && out_dtype == MF_BF16 && slices == 1 && H % 8 == 0 &&
+      (((uintptr_t)y | (uintptr_t)out | (uintptr_t)x | (uintptr_t)shared) & 15) == 0)
     return (int)launch_dep(moe_combine_bf16_vec_kernel, dim3(T, (H / 8 + 255) / 256), dim3(256), 0, stream,
-                           (const __nv_bfloat16*)y, weights, slot_of, (__nv_bfloat16*)out, H, top);
+                           (const __nv_bfloat16*)y, weights, slot_of, (__nv_bfloat16*)out, H, top, ex);
   const dim3 grid(T, (H + 255) / 256);
 #define MC_LAUNCH(TO, TY)                                                                                       \
   return (int)launch_dep(moe_combine_kernel<TO, TY>, grid, dim3(256), 0, stream, (const TY*)y, weights, slot_of, \

@@ -189,12 +189,12 @@ def attention_decode_ex(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Ten
                         n_kv: int, head_dim: int, scale: float, window: int, max_ctx: int, v_dim: int, v_in_k: bool,
                         keep_first: int = 0, sink: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None,
                         gate_ld: int = 0) -> None:
-    """``attention_decode`` with the same options; scratch as ``attention_decode_scratch`` says."""
+    """``attention_decode`` with the same options; scratch as ``attention_decode_scratch`` says for this window."""
     _need_cuda(q, k_pool, v_pool, out, part_o, part_ml, positions, seq_of_token, block_table, sink)
     if q.dtype != torch.bfloat16 or k_pool.dtype != torch.bfloat16:
         raise KernelError("attention_decode_ex: bfloat16 only")
     n = q.shape[0]
-    need_o, need_ml = attention_decode_scratch(n, n_heads, head_dim, max_ctx)
+    need_o, need_ml = attention_decode_scratch(n, n_heads, head_dim, max_ctx, window)
     if part_o.numel() < need_o or part_ml.numel() < need_ml or part_o.dtype != torch.float32:
         raise KernelError("attention_decode_ex: scratch too small")
     check(library().mf_attention_decode_ex(q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), out.data_ptr(),
@@ -521,10 +521,17 @@ def attention_decode_split(head_dim: int) -> int:
     return int(library().mf_attention_decode_split(head_dim))
 
 
-def attention_decode_scratch(n_tokens: int, n_heads: int, head_dim: int, max_ctx: int):
-    """Element counts of the two float32 scratch buffers the decode kernel needs."""
-    splits = (max_ctx + attention_decode_split(head_dim) - 1) // attention_decode_split(head_dim)
+def attention_decode_scratch(n_tokens: int, n_heads: int, head_dim: int, max_ctx: int, window: Optional[int] = None):
+    """Element counts of the two float32 scratch buffers the decode kernel needs; with ``window`` (0: none)
+    those of the launch with options, whose split depends on the window."""
+    split = attention_decode_split(head_dim) if window is None else attention_decode_ex_split(head_dim, window)
+    splits = (max_ctx + split - 1) // split
     return n_tokens * n_heads * splits * head_dim, n_tokens * n_heads * splits * 2
+
+
+def attention_decode_ex_split(head_dim: int, window: int) -> int:
+    """Keys per split of ``attention_decode_ex`` for a lane with this window (0: none)."""
+    return int(library().mf_attention_decode_ex_split(head_dim, window))
 
 
 def attention_decode(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, out: torch.Tensor,

@@ -138,7 +138,7 @@ def options_paged_attention(rt, batch, q, lane, out, n_heads: int, scale: float,
         return
     nd = batch.n_decode
     if nd > 0:
-        n_o, n_ml = ops.attention_decode_scratch(nd, n_heads, need.head_dim, batch.max_ctx)
+        n_o, n_ml = ops.attention_decode_scratch(nd, n_heads, need.head_dim, batch.max_ctx, window)
         ops.attention_decode_ex(q[:nd], lane.k, lane.v, out[:nd], rt.buffer("attn.part_o", (n_o,), torch.float32),
                                 rt.buffer("attn.part_ml", (n_ml,), torch.float32), batch.positions[:nd],
                                 batch.seq_of_token[:nd], table, lane.page_size, n_heads, need.n_kv_heads,
