@@ -757,8 +757,7 @@ def run_rabapel(args) -> int:
     out = {"workload": "rabapel", "dtype": "bf16", "peaks": pk,
            "data": "synthetic: seeded random weights, seeded uniform token ids, random cache contents",
            "fp32_tflops_nominal": round(FP32_TFLOPS_NOMINAL, 1), "sizes": {}}
-    clocks = ClockSampler()
-    clocks.start()
+    sampled = []
     for key in ([args.size] if args.size else sorted(RABAPEL_SIZES)):
         z = RABAPEL_SIZES[key]
         res = {"size": z}
@@ -774,6 +773,9 @@ def run_rabapel(args) -> int:
             for pool in set(engine.cache._k + engine.cache._v):
                 pool.normal_(0.0, 1.0)
             ctx = z["context"]
+            # clocks while the device works: writing and loading a model is host time at idle clocks
+            clocks = ClockSampler()
+            clocks.start()
             t_pre = prefill_device(engine, PREFILL_TOKENS, runs=3, warmup=3)
             sec, launches, _, _ = decode_device(engine, args.batch, ctx, args.steps, args.warmup)
             r = {"prefill_tokens": PREFILL_TOKENS, "prefill_ms": round(t_pre * 1e3, 3),
@@ -783,12 +785,17 @@ def run_rabapel(args) -> int:
                  "weight_bytes_per_step": engine.model.weight_bytes()}
             if not args.skip_points:
                 r["kernels"] = kernel_table(engine, names, PREFILL_TOKENS, args.batch, ctx, 0, pk, extra={"ctx": ctx})
+            r["clocks"] = clocks.stop()
+            sampled.append(r["clocks"])
             ops.check_kernel_status()
             res[which] = r
             del engine
             torch.cuda.empty_cache()
         out["sizes"][key] = res
-    out["clocks"] = clocks.stop()
+    seen = [c for c in sampled if c["sm_mhz"] is not None]
+    out["clocks"] = {"sm_mhz": min(c["sm_mhz"] for c in seen) if seen else None,
+                     "sm_max_mhz": max(c["sm_max_mhz"] for c in seen) if seen else None,
+                     "reasons": sorted({x for c in seen for x in c["reasons"]})}
     print(json.dumps(out))
     return 0
 
