@@ -63,6 +63,45 @@ RB_C = {"architecture": "Rabapel", "vocab": 320, "width": 192, "norm": {"eps": 1
 CONFIGS = {"A": RB_A, "B": RB_B, "C": RB_C}
 
 
+def random_config(seed, big):
+    """A configuration drawn from a seed: two kinds of mixer with sizes, window, base, scale and stretch drawn
+    apart, two to five layers that take either, each with a dense feed-forward, a mixture (1 to 16 experts, 0
+    to 4 identity experts, 1 to 6 chosen, with or without a shared expert) or none.  ``big``: sizes that the
+    tensor-core kernels take among others; else small and odd ones."""
+    rng = np.random.default_rng(seed)
+    pick = lambda xs: xs[int(rng.integers(len(xs)))]
+
+    def mixer():
+        heads = pick([1, 2, 3, 4, 6, 8])
+        dim = pick([16, 32, 48, 64] if big else [4, 8, 12, 20])
+        rot = pick([16, 32, 64] if big else [2, 4, 6, 8])
+        vdim = pick([16, 24, 32, 48, 64, 80] if big else [4, 6, 10, 16])
+        rank = pick([32, 48, 64, 96, 112, 128, 192] if big else [6, 12, 20, 28])
+        window = pick([0, 1, 17, 64, 96, 100, 128, 200, 257])
+        scaling = None if rng.random() < 0.2 else (float(pick([2.0, 4.0, 8.0, 16.0])), int(pick([32, 64, 512, 2048])),
+                                                   float(pick([8.0, 32.0])), float(pick([0.5, 1.0, 2.0])))
+        return _mixer(heads, dim, rot, vdim, rank, float(pick([100.0, 10000.0, 250000.0, 1e6])), window=window,
+                      scale=float(pick([0.05, 0.125, 0.2, (dim + rot) ** -0.5])), scaling=scaling)
+
+    width = pick([64, 96, 128, 160, 192, 256, 384] if big else [24, 40, 56, 72, 100])
+    mixers = [mixer(), mixer()]
+    layers = []
+    for _ in range(int(rng.integers(2, 6))):
+        r = rng.random()
+        if r < 0.4:
+            mlp = _dense(pick([64, 136, 256, 512] if big else [10, 24, 36]))
+        elif r < 0.9:
+            e, ident = int(rng.integers(1, 17)), int(rng.integers(0, 5))
+            mlp = _moe(pick([32, 64, 96, 136] if big else [8, 12, 20]), e, ident, int(rng.integers(1, min(e + ident, 6) + 1)),
+                       shared=pick([0, 64, 128] if big else [0, 12, 16]))
+        else:
+            mlp = None
+        layers.append(_layer(dict(mixers[int(rng.integers(2))]), mlp))
+    return {"architecture": "Rabapel", "vocab": int(pick([50, 101, 256, 1000])), "width": width,
+            "norm": {"eps": float(pick([1e-6, 1e-5]))}, "embedding": {"scale": float(pick([0.5, 1.0, 2.0, 0.3]))},
+            "layers": layers}
+
+
 def tensor_shapes(cfg):
     H = cfg["width"]
     out = [("embed", (cfg["vocab"], H))]

@@ -451,6 +451,43 @@ def test_every_request_decoded_from_its_first_token(models, which, dtype, tmp_pa
     _check(models, which, False, dtype, TT.lockstep(reqs), tmp_path, max_seqs=len(reqs))
 
 
+@pytest.mark.parametrize("seed", range(12))
+def test_configurations_drawn_at_random(seed, tmp_path):
+    """Sizes, layer orders, windows and constants drawn from a seed: whole prompts, portions and a mixed batch
+    with reused pages, both dtypes, against the plain implementation.  Places where a choice of experts is a
+    close call (for the dtype) are left out."""
+    from helpers import write_model_dir
+    from rabapel_helpers import random_config, random_weights
+    big = seed % 2 == 0
+    cfg = random_config(100 + seed, big)
+    w = random_weights(cfg, seed)
+    d = write_model_dir(str(tmp_path / "model"), cfg, w, "bfloat16")
+    w64 = {k: v.astype(np.float64) for k, v in w.items()}
+    reqs = {f"r{i}": prompt(cfg, n, i) for i, n in enumerate([260 + 9 * seed, 170] if big else [97 + seed, 40, 61]) }
+    reqs.update({"one": prompt(cfg, 1, 8), "two": prompt(cfg, 2, 9)})
+    expected, close = {}, {"float32": set(), "bfloat16": set()}
+    for rid, toks in reqs.items():
+        margins = []
+        expected[rid] = P.forward(cfg, w64, toks, margins_out=margins)
+        for dt, least in (("float32", 1e-5), ("bfloat16", 4 * CLOSE_CALL)):
+            close[dt] |= {(rid, int(t)) for m in margins for t in np.nonzero(m < least)[0]}
+    P.ROUND = P.round_bf16
+    try:
+        noise = max(float(np.max(np.abs(P.forward(cfg, w64, toks) - expected[rid]))) for rid, toks in reqs.items())
+    finally:
+        P.ROUND = None
+    scale = max(float(np.max(np.abs(e))) for e in expected.values())
+    limits = {"float32": 1e-4 * max(1.0, scale), "bfloat16": 1.5 * 3.0 * noise}
+    traces = (TT.whole(reqs), TT.portions(reqs), TT.mixed(reqs, max_live=3, seed=seed, decode_last=6, max_portion=50))
+    for i, trace in enumerate(traces):
+        for dtype in ("float32", "bfloat16"):
+            out_dir, _ = _replay(d, dtype, trace, tmp_path / f"{i}{dtype}", max_seqs=3 if i == 2 else 4)
+            got = {k: v for k, v in TT.read_outputs(trace, out_dir, cfg["vocab"]).items() if k not in close[dtype]}
+            assert len(got) > 100
+            worst, where = TT.worst(got, expected)
+            assert worst <= limits[dtype], (cfg, i, dtype, worst, limits[dtype], where)
+
+
 def test_batch_and_cut_do_not_change_a_position(models, tmp_path):
     """float32: a request inside a mixed batch, cut into portions, and alone and whole agree to rounding."""
     d, cfg, reqs, *_ = models[("A", True)]
