@@ -44,7 +44,8 @@ class CacheLayout:
 
     paged: Tuple[GroupLayout, ...]
     state: Tuple[GroupLayout, ...]
-    item_lane: Tuple[Optional[Tuple[str, int, int]], ...]    # ("paged"|"state", group, lane)
+    # ("paged"|"state", group, lane), or a tuple of those for a layer with several needs
+    item_lane: Tuple[Optional[tuple], ...]
 
     def bytes_per_token(self, elt_bytes: int) -> int:
         """Key+value bytes one token adds over all paged lanes
@@ -129,6 +130,11 @@ class CacheManager:
         where = self.layout.item_lane[item]
         if where is None:
             return None
+        if isinstance(where[0], tuple):          # a layer with several needs: its lanes in their order
+            return tuple(self._lane_at(w) for w in where)
+        return self._lane_at(where)
+
+    def _lane_at(self, where):
         kind, g, lane = where
         if kind == "paged":
             return KVLane(self._k[g][lane], self._v[g][lane], g, self.layout.paged[g].need, self.page_size)

@@ -59,4 +59,4 @@ def config_from_dir(model_dir: str) -> ModelConfig:
 
 def _ensure_builtin() -> None:
     # the built-in architectures register themselves on import
-    from ..models import llama, luzinex, notirax, rabapel  # noqa: F401
+    from ..models import ledinex, llama, luzinex, notirax, rabapel  # noqa: F401

@@ -188,6 +188,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
 #pragma unroll
         for (int e = 0; e < 4; e++) {
           float v = s[j][e] * scale_log2;
+          if (opt.softcap > 0.f) v = opt.softcap * 1.4426950408889634f * tanhf(v * (0.6931471805599453f / opt.softcap));
           if (edge) {
             const int key = w_begin + j * 8 + tq * 2 + (e & 1);
             if ((key < lo && key >= keep) || key > pos) v = -INFINITY;
@@ -501,12 +502,12 @@ MF_API int mf_attention_decode_ex(const void* q, const void* k_pool, const void*
                                   float* part_ml, int n_tokens, int n_heads, int n_kv, int hd, const int* positions,
                                   const int* seq_of_token, const int* block_table, int bt_stride, int page_size,
                                   float scale, int window, int max_ctx, int vd, int v_in_k, int keep_first,
-                                  const float* sink, const void* gate, long long gate_ld, cudaStream_t stream) {
+                                  const float* sink, const void* gate, long long gate_ld, float softcap, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   if (hd < 16 || hd > 256 || hd % 16 || n_kv <= 0 || n_heads % n_kv || max_ctx <= 0) return MF_ERR_BAD_ARG;
   if (vd <= 0 || vd > hd || vd % 16 || keep_first < 0 || n_tokens > 65535) return MF_ERR_BAD_ARG;
   PagedView pv{block_table, bt_stride, page_size, n_kv, hd};
-  const AttnOptions opt{vd, v_in_k, keep_first, sink, (const __nv_bfloat16*)gate, gate_ld};
+  const AttnOptions opt{vd, v_in_k, keep_first, sink, (const __nv_bfloat16*)gate, gate_ld, softcap};
   const __nv_bfloat16 *qq = (const __nv_bfloat16*)q, *kk = (const __nv_bfloat16*)k_pool,
                       *vv = (const __nv_bfloat16*)v_pool;
   __nv_bfloat16* oo = (__nv_bfloat16*)out;

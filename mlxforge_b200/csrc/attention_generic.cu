@@ -29,7 +29,7 @@ attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_pool, 
                          T* __restrict__ out, const int* __restrict__ positions,
                          const int* __restrict__ seq_of_token, PagedView pv, int n_heads, float scale,
                          int window, int vd, int v_ld, int keep_first, const float* __restrict__ sink,
-                         const T* __restrict__ gate, int gate_ld) {
+                         const T* __restrict__ gate, int gate_ld, float softcap) {
   extern __shared__ float smem[];
   float* qs = smem;                 // [hd]
   float* ps = smem + pv.head_dim;   // [CHUNK]
@@ -67,6 +67,7 @@ attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_pool, 
       float dot = 0.f;
       for (int d = 0; d < hd; d++) dot = fmaf(qs[d], to_f32<T>(kr[d]), dot);
       s = dot * scale;
+      if (softcap > 0.f) s = softcap * tanhf(s / softcap);
     }
     const float cm = block_max(s, red);
     const float m_new = fmaxf(m, cm);
@@ -109,7 +110,7 @@ static int launch_generic(const void* q, const void* k_pool, const void* v_pool,
                           int n_heads, int n_kv, int hd, const int* positions, const int* seq_of_token,
                           const int* block_table, int bt_stride, int page_size, float scale, int window, int vd,
                           int v_ld, int keep_first, const float* sink, const void* gate, int gate_ld,
-                          cudaStream_t stream) {
+                          float softcap, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (hd <= 0 || hd > 1024 || vd <= 0 || vd > MAX_ACC * CHUNK || v_ld < vd || n_kv <= 0 || n_heads % n_kv)
     return MF_ERR_BAD_ARG;
@@ -121,12 +122,12 @@ static int launch_generic(const void* q, const void* k_pool, const void* v_pool,
   if (dtype == MF_F32)
     attention_generic_kernel<float><<<grid, CHUNK, smem, stream>>>(
         (const float*)q, (const float*)k_pool, (const float*)v_pool, (float*)out, positions, seq_of_token, pv,
-        n_heads, scale, window, vd, v_ld, keep_first, sink, (const float*)gate, gate_ld);
+        n_heads, scale, window, vd, v_ld, keep_first, sink, (const float*)gate, gate_ld, softcap);
   else if (dtype == MF_BF16)
     attention_generic_kernel<__nv_bfloat16><<<grid, CHUNK, smem, stream>>>(
         (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool,
         (__nv_bfloat16*)out, positions, seq_of_token, pv, n_heads, scale, window, vd, v_ld, keep_first, sink,
-        (const __nv_bfloat16*)gate, gate_ld);
+        (const __nv_bfloat16*)gate, gate_ld, softcap);
   else
     return MF_ERR_BAD_DTYPE;
   return (int)cudaGetLastError();
@@ -138,7 +139,7 @@ MF_API int mf_attention_generic(const void* q, const void* k_pool, const void* v
                                 int page_size, float scale, int window, cudaStream_t stream) {
   if (hd > 2 * CHUNK) return MF_ERR_BAD_ARG;
   return launch_generic(q, k_pool, v_pool, out, dtype, T, n_heads, n_kv, hd, positions, seq_of_token, block_table,
-                        bt_stride, page_size, scale, window, hd, hd, 0, nullptr, nullptr, 0, stream);
+                        bt_stride, page_size, scale, window, hd, hd, 0, nullptr, nullptr, 0, 0.f, stream);
 }
 
 // The same with the options above: value width and row stride, kept first keys, sink, output gate.
@@ -146,7 +147,8 @@ MF_API int mf_attention_generic_ex(const void* q, const void* k_pool, const void
                                    int T, int n_heads, int n_kv, int hd, const int* positions,
                                    const int* seq_of_token, const int* block_table, int bt_stride,
                                    int page_size, float scale, int window, int vd, int v_ld, int keep_first,
-                                   const float* sink, const void* gate, int gate_ld, cudaStream_t stream) {
+                                   const float* sink, const void* gate, int gate_ld, float softcap,
+                                   cudaStream_t stream) {
   return launch_generic(q, k_pool, v_pool, out, dtype, T, n_heads, n_kv, hd, positions, seq_of_token, block_table,
-                        bt_stride, page_size, scale, window, vd, v_ld, keep_first, sink, gate, gate_ld, stream);
+                        bt_stride, page_size, scale, window, vd, v_ld, keep_first, sink, gate, gate_ld, softcap, stream);
 }

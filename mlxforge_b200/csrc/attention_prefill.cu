@@ -197,6 +197,15 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
           }
         }
       }
+      if (opt.softcap > 0.f) {
+        const float sc_scale = scale_log2 * 0.6931471805599453f;
+#pragma unroll
+        for (int mt = 0; mt < MT; mt++)
+#pragma unroll
+          for (int j = 0; j < BN / 8; j++)
+#pragma unroll
+            for (int e = 0; e < 4; e++) sc[mt][j][e] = softcap_raw(sc[mt][j][e], sc_scale, opt.softcap);
+      }
       // ---- mask only where the tile touches the diagonal or an end of a window; online softmax
       const bool edge = kt * BN + BN - 1 > w_pos_first || kt * BN < w_lo_last;
       if (edge) {            // a loop of its own under one branch: tiles off the diagonal pay nothing for the mask
@@ -384,13 +393,13 @@ MF_API int mf_attention_prefill_ex(const void* q, const void* k_pool, const void
                                    int table_row0, int n_seqs, int max_q_len, int n_heads, int n_kv, int hd,
                                    const int* block_table, int bt_stride, int page_size, float scale, int window,
                                    int vd, int v_in_k, int keep_first, const float* sink, const void* gate,
-                                   long long gate_ld, cudaStream_t stream) {
+                                   long long gate_ld, float softcap, cudaStream_t stream) {
   if (n_seqs <= 0 || max_q_len <= 0) return 0;
   if (hd < 16 || hd > 256 || hd % 16 || n_kv <= 0 || n_heads % n_kv) return MF_ERR_BAD_ARG;
   if (vd <= 0 || vd > hd || vd % 16 || keep_first < 0) return MF_ERR_BAD_ARG;
   if (n_heads > 65535 || n_seqs > 65535) return MF_ERR_BAD_ARG;
   PagedView pv{block_table, bt_stride, page_size, n_kv, hd};
-  const AttnOptions opt{vd, v_in_k, keep_first, sink, (const __nv_bfloat16*)gate, gate_ld};
+  const AttnOptions opt{vd, v_in_k, keep_first, sink, (const __nv_bfloat16*)gate, gate_ld, softcap};
   const __nv_bfloat16 *qq = (const __nv_bfloat16*)q, *kk = (const __nv_bfloat16*)k_pool,
                       *vv = (const __nv_bfloat16*)v_pool;
   __nv_bfloat16* oo = (__nv_bfloat16*)out;

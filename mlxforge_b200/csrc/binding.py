@@ -65,9 +65,17 @@ _SIGNATURES = {
                          c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P],
     "mf_delta_gates": [_P, _P, _P, c_int, c_int, c_int, c_int, _P],
     "mf_delta_recurrence": [_P, _P, _P, c_int, _P, c_longlong, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P],
-    "mf_delta_output": [_P, _P, c_int, _P, c_float, _P, c_int, c_int, c_int, c_int, _P],
+    "mf_delta_output": [_P, _P, c_int, _P, c_float, _P, c_int, c_int, c_int, c_int, c_int, _P],
+    "mf_delta_gates_ex": [_P, c_int, c_int, c_int, c_float, _P, _P, _P, c_int, c_int, _P, c_int, c_int, c_int, c_int, _P],
+    "mf_gdelta_prepare": [_P, c_int, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P],
+    "mf_gdelta_recurrence": [_P, _P, c_int, _P, c_int, _P, c_longlong, _P, _P, _P, _P, c_int, c_int, c_int, _P],
+    "mf_conv_input": [_P, c_int, c_int, _P, c_int, _P, c_longlong, c_longlong, _P, _P, _P, _P, c_int, _P, c_int, _P],
+    "mf_postnorm_add": [_P, c_int, c_int, _P, c_float, _P, c_float, c_int, _P, c_float, _P],
+    "mf_qk_norm_rope": [_P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, _P, _P, _P,
+                        _P, _P, _P, _P, _P, _P, _P, c_int, c_int, _P, _P, _P, c_int, _P],
+    "mf_rotate_rows": [_P, c_int, c_int, c_int, c_int, c_int, _P, _P, _P, c_float, _P],
     "mf_moe_route": [_P, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, _P, _P, _P, _P],
-    "mf_moe_rows": [_P, _P, _P, c_int, _P, _P, c_int, c_int, c_int, c_int, c_float, c_float, c_float, c_int, _P],
+    "mf_moe_rows": [_P, _P, _P, c_int, _P, _P, c_int, c_int, c_int, c_int, c_float, c_float, c_float, c_int, c_int, _P],
     "mf_moe_combine": [_P, c_int, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P, c_int, _P, _P, _P, c_int, _P],
     "mf_moe_gather_rows": [_P, _P, _P, c_int, c_int, _P],
     "mf_moe_activation": [_P, _P, c_int, c_int, c_float, c_float, c_float, _P],
@@ -82,16 +90,17 @@ _SIGNATURES = {
     "mf_moe_sort": [_P, c_int, c_int, c_int, _P, _P, _P, _P, _P, _P],
     "mf_moe_grouped_ok": [c_int, c_int, c_int],
     "mf_moe_grouped_max_tiles": [c_int, c_int, c_int],
-    "mf_moe_grouped_up": [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_float, _P],
+    "mf_moe_grouped_up": [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_float, c_int,
+                          _P],
     "mf_moe_grouped_down": [_P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P],
     "mf_attention_prefill_ex": [_P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P, c_int, c_int,
-                                c_float, c_int, c_int, c_int, c_int, _P, _P, c_longlong, _P],
+                                c_float, c_int, c_int, c_int, c_int, _P, _P, c_longlong, c_float, _P],
     "mf_attention_decode_ex": [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, _P, _P, _P, c_int, c_int,
-                               c_float, c_int, c_int, c_int, c_int, c_int, _P, _P, c_longlong, _P],
+                               c_float, c_int, c_int, c_int, c_int, c_int, _P, _P, c_longlong, c_float, _P],
     "mf_gated_act": [_P, _P, c_int, c_int, c_int, c_int, c_int, _P],
     "mf_add_rmsnorm_pair": [_P, _P, _P, c_int, _P, _P, c_float, _P, _P, c_int, _P, c_int, c_int, _P],
     "mf_attention_generic_ex": [_P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P, _P, _P, c_int, c_int,
-                                c_float, c_int, c_int, c_int, c_int, _P, _P, c_int, _P],
+                                c_float, c_int, c_int, c_int, c_int, _P, _P, c_int, c_float, _P],
     "mf_rope_store": [_P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P, _P, c_int, c_int, _P, _P, _P, _P,
                       _P, c_int, c_int, _P],
     "mf_latent_prepare": [_P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P, c_float, _P, _P, _P, c_int,
@@ -103,12 +112,14 @@ _SIGNATURES = {
     "mf_head_linear_mma_ok": [c_longlong, c_int, c_int],
     "mf_head_linear_mma": [_P, c_longlong, c_int, _P, _P, c_longlong, c_int, c_int, c_int, c_int, c_int, _P,
                            c_longlong, c_int, c_int, _P],
-    "mf_retention_prepare": [_P, c_int, c_int, c_int, c_int, c_int, c_int, c_float, _P, _P, _P, _P, _P],
+    "mf_retention_prepare": [_P, c_int, c_int, c_int, c_int, c_int, c_int, c_float, _P, _P, _P, _P, c_int, _P, c_int,
+                             c_int, _P],
     "mf_set_retention_rows": [c_int],
     "mf_retention_parts": [c_int, c_int, c_int, c_longlong],
     "mf_retention_recurrence": [_P, _P, c_int, c_longlong, _P, _P, c_longlong, _P, _P, _P, _P, c_longlong, c_int, c_int,
                                 c_int, c_int, _P],
-    "mf_retention_output": [_P, c_int, c_longlong, _P, c_int, c_longlong, c_float, _P, c_int, c_int, c_int, _P],
+    "mf_retention_output": [_P, c_int, c_longlong, _P, c_int, c_longlong, c_float, _P, c_int, c_int, c_int, _P, c_int,
+                            c_int, _P],
 }
 
 MF_ERRORS = {10001: "a size or option this kernel does not take", 10002: "an unsupported dtype"}

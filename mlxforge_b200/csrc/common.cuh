@@ -100,7 +100,8 @@ __device__ __forceinline__ long long paged_offset(const PagedView& pv, int seq, 
 // are the first vd channels of the keys (no value pool is read).  keep_first: with a window, keys at
 // positions below it stay visible to every later query.  sink: one float per query head whose
 // exponential joins the softmax denominator (unscaled; no key, no value).  gate: the output row
-// [n_heads * vd] is multiplied by sigmoid(gate[t * gate_ld + ...]).
+// [n_heads * vd] is multiplied by sigmoid(gate[t * gate_ld + ...]).  softcap > 0: a scaled score s
+// becomes softcap * tanh(s / softcap) before the mask and the softmax.
 struct AttnOptions {
   int vd;
   int v_in_k;
@@ -108,7 +109,13 @@ struct AttnOptions {
   const float* sink;
   const __nv_bfloat16* gate;
   long long gate_ld;
+  float softcap;
 };
+// A raw dot product d (not yet scaled) under a soft cap, returned in the same unscaled units, so that
+// the kernel's own multiplication by the scale gives cap * tanh(d * scale / cap).
+__device__ __forceinline__ float softcap_raw(float d, float scale, float cap) {
+  return cap * tanhf(d * (scale / cap)) / scale;
+}
 
 // Offset of the first of 16 consecutive positions [pos16, pos16 + 16), pos16 a multiple
 // of 16: they share a page because the page size is a multiple of 16.  Rows of the
@@ -197,6 +204,12 @@ enum MfKernel {
   MF_K_RETENTION_OUTPUT,      // per-head norm of the read-out and the gate
   MF_K_UNARY_ACT,             // an activation applied to every element (a feed-forward without a gate)
   MF_K_GEMM_TC_ACT,           // many-row product, tcgen05, with that activation in its epilogue
+  MF_K_CONV_INPUT,            // a sublayer's input: the stream plus its short causal convolution
+  MF_K_POSTNORM_ADD,          // RMS norm of a sublayer's output (or of two branches' weighted sum) added to the stream
+  MF_K_QK_NORM_ROPE,          // biases, whole-projection norms, rotation of queries, keys and values, the cache write
+  MF_K_ROTATE_ROWS,           // heads of a row turned by the position (an attention output turned back)
+  MF_K_GDELTA_PREPARE,        // operands of the generalized delta rule: unit keys, removal rates, tanh of the low rank
+  MF_K_GDELTA_RECURRENCE,     // its state, token after token
   MF_K_COUNT
 };
 extern unsigned long long g_mf_kernel_launches[MF_K_COUNT];

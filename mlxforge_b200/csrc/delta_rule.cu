@@ -325,10 +325,12 @@ delta_recurrence_staged_kernel(const float* __restrict__ qkv, const float* __res
 
 // ------------------------------------------------------------------ read-out norm and gate
 // out[t, h, c] = o[t, h, c] / sqrt(mean_c o^2 + eps) * w[c] * gate[t, h, c]; a warp per (token, head).
+// w_per_head: the weight is [n_heads * vdim] (a row of its own for every head) instead of [vdim].
 template <typename TO>
 __global__ void __launch_bounds__(256)
 delta_output_kernel(const float* __restrict__ o, const float* __restrict__ gate, int gate_ld,
-                    const float* __restrict__ w, float eps, TO* __restrict__ out, int n_heads, int vdim, int total) {
+                    const float* __restrict__ w, float eps, TO* __restrict__ out, int n_heads, int vdim, int total,
+                    int w_per_head) {
   const int item = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (item >= total) return;
   const int lane = threadIdx.x & 31;
@@ -339,7 +341,8 @@ delta_output_kernel(const float* __restrict__ o, const float* __restrict__ gate,
   ss = warp_sum(ss);
   const float inv = 1.0f / sqrtf(ss / (float)vdim + eps);
   const float* g = gate + (long long)t * gate_ld + h * vdim;
-  for (int c = lane; c < vdim; c += 32) out[(long long)item * vdim + c] = from_f32<TO>(row[c] * inv * w[c] * g[c]);
+  const float* wh = w + (w_per_head ? h * vdim : 0);
+  for (int c = lane; c < vdim; c += 32) out[(long long)item * vdim + c] = from_f32<TO>(row[c] * inv * wh[c] * g[c]);
 }
 
 // ------------------------------------------------------------------ entry points
@@ -437,17 +440,195 @@ MF_API int mf_delta_recurrence(const float* qkv, const float* beta, const float*
 }
 
 MF_API int mf_delta_output(const float* o, const float* gate, int gate_ld, const float* w, float eps, void* out,
-                           int out_dtype, int T, int n_heads, int vdim, cudaStream_t stream) {
+                           int out_dtype, int T, int n_heads, int vdim, int w_per_head, cudaStream_t stream) {
   if (T <= 0) return 0;
   const int total = T * n_heads;
   const unsigned blocks = (unsigned)((total + 7) / 8);
   mf_count(MF_K_DELTA_OUTPUT);
   if (out_dtype == MF_F32)
-    delta_output_kernel<float><<<blocks, 256, 0, stream>>>(o, gate, gate_ld, w, eps, (float*)out, n_heads, vdim, total);
+    delta_output_kernel<float><<<blocks, 256, 0, stream>>>(o, gate, gate_ld, w, eps, (float*)out, n_heads, vdim, total,
+                                                           w_per_head);
   else if (out_dtype == MF_BF16)
     delta_output_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(o, gate, gate_ld, w, eps, (__nv_bfloat16*)out,
-                                                                   n_heads, vdim, total);
+                                                                   n_heads, vdim, total, w_per_head);
   else
     return MF_ERR_BAD_DTYPE;
+  return (int)cudaGetLastError();
+}
+
+// ------------------------------------------------------------------ decays and gates from rows of their own
+// ag [T, n_heads * dim + n_gate] from two inputs.  Decays, one per head and key channel: the input has one
+// number per head and channel, or (per_head) one per head that all its channels share;
+//   kind 0: exp(-exp(a_log[h]) softplus(x + bias)) ,   kind 1: exp(-c sigmoid(x + bias))
+// (bias indexed like the input).  Gates: sigmoid (gate_act 0) or SiLU (1) of gate_in.
+__global__ void delta_gates_ex_kernel(const float* __restrict__ decay_in, int decay_ld, int per_head, int kind, float c,
+                                      const float* __restrict__ a_log, const float* __restrict__ bias,
+                                      const float* __restrict__ gate_in, int gate_ld, int gate_act,
+                                      float* __restrict__ ag, int n_decay, int dim, int width, long long total) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const long long t = i / width;
+  const int j = (int)(i - t * width);
+  if (j < n_decay) {
+    const int h = j / dim, src = per_head ? h : j;
+    const float x = decay_in[t * decay_ld + src] + (bias ? bias[src] : 0.f);
+    ag[i] = kind == 0 ? expf(-expf(a_log[h]) * dr_softplus(x)) : expf(-c * dr_sigmoid(x));
+  } else {
+    const float x = gate_in[t * gate_ld + (j - n_decay)];
+    ag[i] = gate_act == 0 ? dr_sigmoid(x) : x * dr_sigmoid(x);
+  }
+}
+
+MF_API int mf_delta_gates_ex(const float* decay_in, int decay_ld, int per_head, int kind, float c, const float* a_log,
+                             const float* bias, const float* gate_in, int gate_ld, int gate_act, float* ag, int T,
+                             int n_heads, int dim, int n_gate, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (kind < 0 || kind > 1 || (kind == 0 && !a_log) || gate_act < 0 || gate_act > 1) return MF_ERR_BAD_ARG;
+  const int width = n_heads * dim + n_gate;
+  const long long total = (long long)T * width;
+  mf_count(MF_K_DELTA_GATES);
+  delta_gates_ex_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(
+      decay_in, decay_ld, per_head, kind, c, a_log, bias, gate_in, gate_ld, gate_act, ag, n_heads * dim, dim, width, total);
+  return (int)cudaGetLastError();
+}
+
+// ------------------------------------------------------------------ generalized delta rule
+// Per head, with a 32-bit state S [dim, dim]:
+//   S_t = diag(w_t) S_(t-1) - (a_t * u_t) (u_t^T S_(t-1)) + k_t v_t^T ,   o_t = S_t^T r_t
+// with u = k / sqrt(sum k^2 + 1e-6) the unit key of the head; the decay and the removal both read the
+// OLD state.  Column c of S needs only column c, so the recurrence is parallel over (sequence, head,
+// column) and serial in time, as above.
+//
+// gdelta_prepare: proj [T, ld] 32-bit holds r | k | v | a | (gate) | low, each n = n_heads * dim wide but
+// the last (`rank`).  ops_out [T, 4 n] gets r | k | u | a u with a = sigmoid(a + a_bias); `low` [T, rank]
+// gets tanh of the low-rank activations in the compute dtype.
+template <typename TL>
+__global__ void __launch_bounds__(256)
+gdelta_prepare_kernel(const float* __restrict__ proj, int ld, const float* __restrict__ a_bias,
+                      float* __restrict__ ops_out, TL* __restrict__ low, int low_off, int rank, int n_heads, int dim) {
+  const long long t = blockIdx.x;
+  const int n = n_heads * dim;
+  const float* p = proj + t * ld;
+  float* o = ops_out + t * 4 * n;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  for (int h = warp; h < n_heads; h += nwarps) {
+    const float* k = p + n + h * dim;
+    float ss = 0.f;
+    for (int d = lane; d < dim; d += 32) ss = fmaf(k[d], k[d], ss);
+    ss = warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss + 1e-6f);
+    for (int d = lane; d < dim; d += 32) {
+      const int c = h * dim + d;
+      const float u = k[d] * inv;
+      o[c] = p[c];
+      o[n + c] = k[d];
+      o[2 * n + c] = u;
+      o[3 * n + c] = dr_sigmoid(p[3 * n + c] + (a_bias ? a_bias[c] : 0.f)) * u;
+    }
+  }
+  for (int i = threadIdx.x; i < rank; i += blockDim.x) low[t * rank + i] = from_f32<TL>(tanhf(p[low_off + i]));
+}
+
+MF_API int mf_gdelta_prepare(const float* proj, int ld, const float* a_bias, float* ops_out, void* low, int low_dtype,
+                             int low_off, int rank, int T, int n_heads, int dim, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  mf_count(MF_K_GDELTA_PREPARE);
+  if (low_dtype == MF_F32)
+    gdelta_prepare_kernel<float><<<T, 256, 0, stream>>>(proj, ld, a_bias, ops_out, (float*)low, low_off, rank, n_heads, dim);
+  else if (low_dtype == MF_BF16)
+    gdelta_prepare_kernel<__nv_bfloat16><<<T, 256, 0, stream>>>(proj, ld, a_bias, ops_out, (__nv_bfloat16*)low, low_off,
+                                                                rank, n_heads, dim);
+  else
+    return MF_ERR_BAD_DTYPE;
+  return (int)cudaGetLastError();
+}
+
+// ops [T, 4 n]: r | k | u | a u;  w [T, w_ld]: the decays of head h at column h * dim;  v [T, v_ld]: the
+// values of head h at column h * dim (32-bit).  Channel d of a column belongs to lane d / DPT of its eight.
+template <int DPT>
+__global__ void __launch_bounds__(DR_THREADS)
+gdelta_recurrence_kernel(const float* __restrict__ ops, const float* __restrict__ w, int w_ld,
+                         const float* __restrict__ v, int v_ld, float* __restrict__ state, long long state_stride,
+                         const int* __restrict__ seq_q_start, const int* __restrict__ seq_q_len,
+                         const int* __restrict__ slots, float* __restrict__ o_out, int n_heads, int dim) {
+  const int seq = blockIdx.x, h = blockIdx.y;
+  const int col = blockIdx.z * DR_COLS + threadIdx.x / DR_LANES;
+  const int part = threadIdx.x % DR_LANES;
+  const int n = n_heads * dim;
+  const int start = seq_q_start[seq], len = seq_q_len[seq];
+  const bool live = col < dim;
+  float* S = state + (long long)slots[seq] * state_stride + (long long)h * dim * dim;
+  float s[DPT];
+#pragma unroll
+  for (int i = 0; i < DPT; i++) {
+    const int d = part * DPT + i;
+    s[i] = (live && d < dim) ? S[(long long)d * dim + col] : 0.f;
+  }
+  float rd[DPT], kd[DPT], ud[DPT], ad[DPT], wd[DPT];
+  float vv = 0.f;
+  auto fetch = [&](int t) {
+    const float* row = ops + (long long)t * 4 * n + h * dim;
+#pragma unroll
+    for (int i = 0; i < DPT; i++) {
+      const int d = part * DPT + i;
+      const bool in = d < dim;
+      rd[i] = in ? row[d] : 0.f;
+      kd[i] = in ? row[n + d] : 0.f;
+      ud[i] = in ? row[2 * n + d] : 0.f;
+      ad[i] = in ? row[3 * n + d] : 0.f;
+      wd[i] = in ? w[(long long)t * w_ld + h * dim + d] : 0.f;
+    }
+    vv = live ? v[(long long)t * v_ld + h * dim + col] : 0.f;
+  };
+  if (len > 0) fetch(start);
+  for (int t = start; t < start + len; t++) {
+    float rc[DPT], kc[DPT], uc[DPT], ac[DPT], wc[DPT];
+#pragma unroll
+    for (int i = 0; i < DPT; i++) {
+      rc[i] = rd[i];
+      kc[i] = kd[i];
+      uc[i] = ud[i];
+      ac[i] = ad[i];
+      wc[i] = wd[i];
+    }
+    const float vc = vv;
+    if (t + 1 < start + len) fetch(t + 1);        // the next token's operands are on their way meanwhile
+    float dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < DPT; i++) dot = fmaf(s[i], uc[i], dot);
+#pragma unroll
+    for (int off = 1; off < DR_LANES; off <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, off);
+    float o = 0.f;
+#pragma unroll
+    for (int i = 0; i < DPT; i++) {
+      s[i] = fmaf(kc[i], vc, fmaf(-ac[i], dot, wc[i] * s[i]));
+      o = fmaf(s[i], rc[i], o);
+    }
+#pragma unroll
+    for (int off = 1; off < DR_LANES; off <<= 1) o += __shfl_xor_sync(0xffffffffu, o, off);
+    if (live && part == 0) o_out[(long long)t * n + h * dim + col] = o;
+  }
+#pragma unroll
+  for (int i = 0; i < DPT; i++) {
+    const int d = part * DPT + i;
+    if (live && d < dim) S[(long long)d * dim + col] = s[i];
+  }
+}
+
+MF_API int mf_gdelta_recurrence(const float* ops, const float* w, int w_ld, const float* v, int v_ld, float* state,
+                                long long state_stride, const int* seq_q_start, const int* seq_q_len, const int* slots,
+                                float* o_out, int n_seqs, int n_heads, int dim, cudaStream_t stream) {
+  if (n_seqs <= 0) return 0;
+  if (dim <= 0 || dim > 16 * DR_LANES || n_heads <= 0 || n_heads > 65535) return MF_ERR_BAD_ARG;
+  dim3 grid(n_seqs, n_heads, (dim + DR_COLS - 1) / DR_COLS);
+  mf_count(MF_K_GDELTA_RECURRENCE);
+#define GD_LAUNCH(DPT)                                                                                            \
+  gdelta_recurrence_kernel<DPT><<<grid, DR_THREADS, 0, stream>>>(ops, w, w_ld, v, v_ld, state, state_stride,      \
+                                                                 seq_q_start, seq_q_len, slots, o_out, n_heads, dim)
+  const int per = (dim + DR_LANES - 1) / DR_LANES;
+  if (per <= 4) GD_LAUNCH(4);
+  else if (per <= 8) GD_LAUNCH(8);
+  else GD_LAUNCH(16);
+#undef GD_LAUNCH
   return (int)cudaGetLastError();
 }

@@ -14,7 +14,8 @@ const char* const kNames[MF_K_COUNT] = {
     "moe_route",        "moe_rows",         "moe_combine",      "moe_sort",         "moe_grouped",
     "rope_store",       "norm_pair",        "latent_prepare",   "latent_query",     "head_linear",
     "head_linear_mma",  "retention_prepare", "retention_recurrence", "retention_chunked", "retention_output",
-    "unary_act",        "gemm_tc_act",
+    "unary_act",        "gemm_tc_act",      "conv_input",       "postnorm_add",     "qk_norm_rope",
+    "rotate_rows",      "gdelta_prepare",   "gdelta_recurrence",
 };
 int g_sm_count[MF_MAX_DEVICES] = {};
 }  // namespace

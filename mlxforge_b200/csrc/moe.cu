@@ -38,7 +38,8 @@ moe_route_kernel(const float* __restrict__ z, int ldz, int E, int n_groups, int 
   float* sel = s + E;
   float* gs = sel + E;
   const float* zr = z + (long long)t * ldz;
-  if (mode == 1) {
+  const bool renorm = (mode & 2) != 0;       // the chosen weights divided by their sum (+ 1e-20)
+  if (mode & 1) {
     float m = -INFINITY;
     for (int e = lane; e < E; e += 32) m = fmaxf(m, zr[e]);
     m = warp_max(m);
@@ -86,6 +87,7 @@ moe_route_kernel(const float* __restrict__ z, int ldz, int E, int n_groups, int 
       __syncwarp();
     }
   }
+  float chosen_sum = 0.f;
   for (int k = 0; k < top; k++) {
     float best = -INFINITY;
     int bi = -1;
@@ -101,16 +103,23 @@ moe_route_kernel(const float* __restrict__ z, int ldz, int E, int n_groups, int 
     if (lane == 0) {
       ids[(long long)t * top + k] = bi < 0 ? 0 : bi;
       weights[(long long)t * top + k] = bi < 0 ? 0.f : s[bi] * route_scale;
-      if (bi >= 0) sel[bi] = -INFINITY;
+      if (bi >= 0) {
+        chosen_sum += s[bi];
+        sel[bi] = -INFINITY;
+      }
     }
     __syncwarp();
+  }
+  if (renorm && lane == 0) {
+    const float inv = 1.0f / (chosen_sum + 1e-20f);
+    for (int k = 0; k < top; k++) weights[(long long)t * top + k] *= inv;
   }
 }
 
 MF_API int mf_moe_route(const float* z, int ldz, int T, int E, int n_groups, int keep, int top, float route_scale,
                         int mode, const float* bias, int* ids, float* weights, cudaStream_t stream) {
   if (T <= 0) return 0;
-  if (E <= 0 || top <= 0 || top > E || ldz < E || mode < 0 || mode > 1) return MF_ERR_BAD_ARG;
+  if (E <= 0 || top <= 0 || top > E || ldz < E || mode < 0 || mode > 3) return MF_ERR_BAD_ARG;
   if (n_groups > 0 && (E % n_groups || keep < 1 || keep > n_groups || (long long)keep * (E / n_groups) < top))
     return MF_ERR_BAD_ARG;
   const int per_warp = 2 * E + (n_groups > 0 ? n_groups : 1);
@@ -132,7 +141,7 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 moe_rows_kernel(const T* __restrict__ x, const T* __restrict__ w_gu, const T* __restrict__ w_down,
                 const int* __restrict__ ids, float* __restrict__ y, int H, int ff, int top, float limit, float alpha,
-                float up_off, int n_real) {
+                float up_off, int n_real, int act_kind) {
   extern __shared__ float sm[];
   float* xs = sm;            // [H]
   float* act = sm + H;       // [MOE_SLICE]
@@ -145,7 +154,9 @@ moe_rows_kernel(const T* __restrict__ x, const T* __restrict__ w_gu, const T* __
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
   for (int i = threadIdx.x; i < H; i += blockDim.x) xs[i] = to_f32<T>(x[(long long)t * H + i]);
   __syncthreads();
-  const T* wg = w_gu + (long long)e * 2 * ff * H;
+  // act_kind >= 0: an expert without a gate, down(act(up x)); its first matrix is [ff, H] alone
+  const bool gated = act_kind < 0;
+  const T* wg = w_gu + (long long)e * (gated ? 2 : 1) * ff * H;
   const T* wu = wg + (long long)ff * H;
   for (int f = warp; f < fn; f += nwarps) {
     const T* rg = wg + (long long)(f0 + f) * H;
@@ -153,11 +164,12 @@ moe_rows_kernel(const T* __restrict__ x, const T* __restrict__ w_gu, const T* __
     float g = 0.f, u = 0.f;
     for (int i = lane; i < H; i += 32) {
       g = fmaf(xs[i], to_f32<T>(rg[i]), g);
-      u = fmaf(xs[i], to_f32<T>(ru[i]), u);
+      if (gated) u = fmaf(xs[i], to_f32<T>(ru[i]), u);
     }
     g = warp_sum(g);
     u = warp_sum(u);
-    if (lane == 0) {
+    if (lane == 0 && !gated) act[f] = to_f32<T>(from_f32<T>(gate_act(g, act_kind)));
+    else if (lane == 0) {
       g = fminf(g, limit);
       u = fminf(fmaxf(u, -limit), limit);
       // the activation is rounded where a product in the compute dtype would read it
@@ -193,7 +205,7 @@ __device__ __forceinline__ float moe_dot8(const uint4 w, const float* xv) {
 __global__ void __launch_bounds__(256)
 moe_rows_bf16_vec_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w_gu,
                          const __nv_bfloat16* __restrict__ w_down, const int* __restrict__ ids, float* __restrict__ y,
-                         int H, int ff, int top, float limit, float alpha, float up_off, int n_real) {
+                         int H, int ff, int top, float limit, float alpha, float up_off, int n_real, int act_kind) {
   extern __shared__ __align__(16) float sm[];
   float* xs = sm;            // [H]
   float* act = sm + H;       // [MOE_SLICE]
@@ -207,23 +219,25 @@ moe_rows_bf16_vec_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat1
   for (int i = threadIdx.x; i < H; i += blockDim.x) xs[i] = __bfloat162float(x[(long long)t * H + i]);
   if (threadIdx.x < MOE_SLICE) act[threadIdx.x] = 0.f;
   __syncthreads();
-  const __nv_bfloat16* wg = w_gu + (long long)e * 2 * ff * H;
+  const bool gated = act_kind < 0;
+  const __nv_bfloat16* wg = w_gu + (long long)e * (gated ? 2 : 1) * ff * H;
   const __nv_bfloat16* wu = wg + (long long)ff * H;
   for (int f = warp; f < fn; f += nwarps) {
     const uint4* rg = reinterpret_cast<const uint4*>(wg + (long long)(f0 + f) * H);
     const uint4* ru = reinterpret_cast<const uint4*>(wu + (long long)(f0 + f) * H);
     float g = 0.f, u = 0.f;
     for (int i = lane; i < H / 8; i += 32) {
-      const uint4 a = rg[i], b = ru[i];
+      const uint4 a = rg[i];
       float xv[8];
       *reinterpret_cast<float4*>(xv) = *reinterpret_cast<const float4*>(xs + 8 * i);
       *reinterpret_cast<float4*>(xv + 4) = *reinterpret_cast<const float4*>(xs + 8 * i + 4);
       g += moe_dot8(a, xv);
-      u += moe_dot8(b, xv);
+      if (gated) u += moe_dot8(ru[i], xv);
     }
     g = warp_sum(g);
     u = warp_sum(u);
-    if (lane == 0) {
+    if (lane == 0 && !gated) act[f] = __bfloat162float(__float2bfloat16_rn(gate_act(g, act_kind)));
+    else if (lane == 0) {
       g = fminf(g, limit);
       u = fminf(fmaxf(u, -limit), limit);
       act[f] = __bfloat162float(__float2bfloat16_rn(g * moe_sigmoid(alpha * g) * (u + up_off)));
@@ -249,11 +263,11 @@ moe_rows_bf16_vec_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat1
 MF_API int mf_moe_rows_slices(int ff) { return (ff + MOE_SLICE - 1) / MOE_SLICE; }
 
 MF_API int mf_moe_rows(const void* x, const void* w_gu, const void* w_down, int dtype, const int* ids, float* y, int T,
-                       int H, int ff, int top, float limit, float alpha, float up_off, int n_real,
+                       int H, int ff, int top, float limit, float alpha, float up_off, int n_real, int act_kind,
                        cudaStream_t stream) {
   if (T <= 0) return 0;
   const size_t smem = (size_t)(H + MOE_SLICE) * sizeof(float);
-  if (smem > 200 * 1024 || top > 65535) return MF_ERR_BAD_ARG;
+  if (smem > 200 * 1024 || top > 65535 || act_kind >= MF_ACT_COUNT) return MF_ERR_BAD_ARG;
   const dim3 grid(T, top, mf_moe_rows_slices(ff));
   mf_count(MF_K_MOE_ROWS);
 #define MR_LAUNCH(KERNEL, TT)                                                                                      \
@@ -263,7 +277,7 @@ MF_API int mf_moe_rows(const void* x, const void* w_gu, const void* w_down, int 
       if (e != cudaSuccess) return (int)e;                                                                         \
     }                                                                                                              \
     return (int)launch_dep(KERNEL, grid, dim3(256), smem, stream, (const TT*)x, (const TT*)w_gu, (const TT*)w_down, \
-                           ids, y, H, ff, top, limit, alpha, up_off, n_real);                                      \
+                           ids, y, H, ff, top, limit, alpha, up_off, n_real, act_kind);                            \
   } while (0)
   if (dtype == MF_F32) MR_LAUNCH(moe_rows_kernel<float>, float);
   if (dtype == MF_BF16) {

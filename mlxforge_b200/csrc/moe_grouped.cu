@@ -156,24 +156,28 @@ __device__ __forceinline__ void mg_tile(float (&acc)[NB][MG_BN / 8][4], int K, A
   }
 }
 
+// NB 2: gate and up tiles side by side and the gated activation; NB 1: an expert without a gate, whose
+// first matrix is [ff, H] alone, and the activation `act_kind` of its sums.
+template <int NB>
 __global__ void __launch_bounds__(128)
 moe_grouped_up_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w_gu,
                       const int* __restrict__ row_token, const int* __restrict__ meta, const int* __restrict__ tiles,
-                      __nv_bfloat16* __restrict__ act, int H, int ff, float limit, float alpha, float up_off) {
+                      __nv_bfloat16* __restrict__ act, int H, int ff, float limit, float alpha, float up_off,
+                      int act_kind) {
   extern __shared__ __align__(16) __nv_bfloat16 mg_smem[];
   __nv_bfloat16* As = mg_smem;
   __nv_bfloat16* Bs = mg_smem + MG_STAGES * MG_BM * MG_LD;
   if ((int)blockIdx.x >= meta[0]) return;
   const int e = tiles[3 * blockIdx.x], row_first = tiles[3 * blockIdx.x + 1], rows = tiles[3 * blockIdx.x + 2];
   const int n0 = blockIdx.y * MG_BN;
-  const __nv_bfloat16* wg = w_gu + (long long)e * 2 * ff * H;
+  const __nv_bfloat16* wg = w_gu + (long long)e * NB * ff * H;
   const __nv_bfloat16* wu = wg + (long long)ff * H;
-  float acc[2][MG_BN / 8][4];
+  float acc[NB][MG_BN / 8][4];
 #pragma unroll
-  for (int b = 0; b < 2; b++)
+  for (int b = 0; b < NB; b++)
 #pragma unroll
     for (int nt = 0; nt < MG_BN / 8; nt++) acc[b][nt][0] = acc[b][nt][1] = acc[b][nt][2] = acc[b][nt][3] = 0.f;
-  mg_tile<2>(acc, H,
+  mg_tile<NB>(acc, H,
              [&](int r) { return r < rows ? x + (long long)row_token[row_first + r] * H : nullptr; },
              [&](int n) {
                const int col = n0 + (n & (MG_BN - 1));
@@ -194,8 +198,12 @@ moe_grouped_up_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* 
       float v[2];
 #pragma unroll
       for (int j = 0; j < 2; j++) {
+        if (NB == 1) {
+          v[j] = gate_act(acc[0][nt][half * 2 + j], act_kind);
+          continue;
+        }
         const float g = fminf(acc[0][nt][half * 2 + j], limit);
-        const float u = fminf(fmaxf(acc[1][nt][half * 2 + j], -limit), limit);
+        const float u = fminf(fmaxf(acc[NB - 1][nt][half * 2 + j], -limit), limit);
         v[j] = g * (1.0f / (1.0f + __expf(-alpha * g))) * (u + up_off);
       }
       *reinterpret_cast<__nv_bfloat162*>(act + (long long)(row_first + r) * ff + col) = __floats2bfloat162_rn(v[0], v[1]);
@@ -242,7 +250,7 @@ MF_API int mf_moe_grouped_max_tiles(int T, int top, int E) { return (T * top + M
 
 MF_API int mf_moe_grouped_up(const void* x, const void* w_gu, const int* row_token, const int* meta, const int* tiles,
                              void* act, int T, int H, int ff, int E, int top, float limit, float alpha, float up_off,
-                             cudaStream_t stream) {
+                             int act_kind, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (!mf_moe_grouped_ok(H, ff, E)) return MF_ERR_BAD_ARG;
   dim3 grid(mf_moe_grouped_max_tiles(T, top, E), (ff + MG_BN - 1) / MG_BN);
@@ -250,14 +258,22 @@ MF_API int mf_moe_grouped_up(const void* x, const void* w_gu, const int* row_tok
   const size_t smem = (size_t)MG_STAGES * (MG_BM + 2 * MG_BN) * MG_LD * sizeof(__nv_bfloat16);
   static DeviceOnce once;
   const int dev = mf_current_device();
-  if (dev < 0) return MF_ERR_BAD_ARG;
+  if (dev < 0 || act_kind >= MF_ACT_COUNT) return MF_ERR_BAD_ARG;
   if (!once.done[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(moe_grouped_up_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(moe_grouped_up_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(moe_grouped_up_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     once.done[dev] = true;
   }
-  moe_grouped_up_kernel<<<grid, 128, smem, stream>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w_gu, row_token, meta,
-                                                  tiles, (__nv_bfloat16*)act, H, ff, limit, alpha, up_off);
+  if (act_kind < 0)
+    moe_grouped_up_kernel<2><<<grid, 128, smem, stream>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w_gu, row_token,
+                                                          meta, tiles, (__nv_bfloat16*)act, H, ff, limit, alpha, up_off,
+                                                          act_kind);
+  else
+    moe_grouped_up_kernel<1><<<grid, 128, smem, stream>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w_gu, row_token,
+                                                          meta, tiles, (__nv_bfloat16*)act, H, ff, limit, alpha, up_off,
+                                                          act_kind);
   return (int)cudaGetLastError();
 }
 

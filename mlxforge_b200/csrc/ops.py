@@ -146,7 +146,7 @@ def attention_generic_ex(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Te
                          positions: torch.Tensor, seq_of_token: torch.Tensor, block_table: torch.Tensor,
                          page_size: int, n_heads: int, n_kv: int, head_dim: int, scale: float, window: int,
                          v_dim: int, v_ld: int, keep_first: int = 0, sink: Optional[torch.Tensor] = None,
-                         gate: Optional[torch.Tensor] = None, gate_ld: int = 0) -> None:
+                         gate: Optional[torch.Tensor] = None, gate_ld: int = 0, softcap: float = 0.0) -> None:
     """The block-per-token attention with its options: values ``v_dim`` wide in rows ``v_ld`` apart
     (``v_pool`` may be ``k_pool``), the first ``keep_first`` keys kept beside the window, a sink per head in
     the softmax denominator, the output times sigmoid(``gate``) (rows ``gate_ld`` apart)."""
@@ -155,7 +155,7 @@ def attention_generic_ex(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Te
                                             dtype_code(q), q.shape[0], n_heads, n_kv, head_dim, positions.data_ptr(),
                                             seq_of_token.data_ptr(), block_table.data_ptr(), block_table.shape[1],
                                             page_size, scale, window, v_dim, v_ld, keep_first, _ptr(sink),
-                                            _ptr(gate), gate_ld, _stream()), "attention_generic")
+                                            _ptr(gate), gate_ld, float(softcap or 0.0), _stream()), "attention_generic")
 
 
 def attention_tc_ok(head_dim: int, v_dim: int, page_size: int) -> bool:
@@ -169,7 +169,7 @@ def attention_prefill_ex(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Te
                          table_row0: int, max_q_len: int, block_table: torch.Tensor, page_size: int, n_heads: int,
                          n_kv: int, head_dim: int, scale: float, window: int, v_dim: int, v_in_k: bool,
                          keep_first: int = 0, sink: Optional[torch.Tensor] = None,
-                         gate: Optional[torch.Tensor] = None, gate_ld: int = 0) -> None:
+                         gate: Optional[torch.Tensor] = None, gate_ld: int = 0, softcap: float = 0.0) -> None:
     """``attention_prefill`` with options: values ``v_dim`` wide (``v_in_k``: the first channels of the keys),
     kept first keys, a sink per head, the output times sigmoid(``gate``).  bfloat16, the mma.sync kernel."""
     _need_cuda(q, k_pool, v_pool, out, seq_q_start, seq_q_len, seq_ctx_len, block_table, sink)
@@ -180,7 +180,7 @@ def attention_prefill_ex(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Te
                                             table_row0, seq_q_len.shape[0], max_q_len, n_heads, n_kv, head_dim,
                                             block_table.data_ptr(), block_table.shape[1], page_size, scale, window,
                                             v_dim, int(v_in_k), keep_first, _ptr(sink), _ptr(gate), gate_ld,
-                                            _stream()), "attention_prefill_ex")
+                                            float(softcap or 0.0), _stream()), "attention_prefill_ex")
 
 
 def attention_decode_ex(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, out: torch.Tensor,
@@ -188,7 +188,7 @@ def attention_decode_ex(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Ten
                         seq_of_token: torch.Tensor, block_table: torch.Tensor, page_size: int, n_heads: int,
                         n_kv: int, head_dim: int, scale: float, window: int, max_ctx: int, v_dim: int, v_in_k: bool,
                         keep_first: int = 0, sink: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None,
-                        gate_ld: int = 0) -> None:
+                        gate_ld: int = 0, softcap: float = 0.0) -> None:
     """``attention_decode`` with the same options; scratch as ``attention_decode_scratch`` says for this window."""
     _need_cuda(q, k_pool, v_pool, out, part_o, part_ml, positions, seq_of_token, block_table, sink)
     if q.dtype != torch.bfloat16 or k_pool.dtype != torch.bfloat16:
@@ -201,7 +201,8 @@ def attention_decode_ex(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Ten
                                            part_o.data_ptr(), part_ml.data_ptr(), n, n_heads, n_kv, head_dim,
                                            positions.data_ptr(), seq_of_token.data_ptr(), block_table.data_ptr(),
                                            block_table.shape[1], page_size, scale, window, max_ctx, v_dim,
-                                           int(v_in_k), keep_first, _ptr(sink), _ptr(gate), gate_ld, _stream()),
+                                           int(v_in_k), keep_first, _ptr(sink), _ptr(gate), gate_ld,
+                                           float(softcap or 0.0), _stream()),
           "attention_decode_ex", launches=2)
 
 
@@ -274,11 +275,15 @@ def head_linear_mma(x: torch.Tensor, x_ld: int, x_hs: int, w: torch.Tensor, out:
 
 
 def retention_prepare(proj: torch.Tensor, n_heads: int, dim: int, rot: int, k_scale: float, positions: torch.Tensor,
-                      inv_f, inv_d, qk: torch.Tensor) -> None:
-    """Rows [queries | keys | ...] -> 32-bit [T, 2 heads dim]: both rotated, keys times ``k_scale``."""
-    _need_cuda(proj, qk)
+                      inv_f, inv_d, qk: torch.Tensor, silu: bool = False, v_out: Optional[torch.Tensor] = None,
+                      v_off: int = 0) -> None:
+    """Rows [queries | keys | ...] -> 32-bit [T, 2 heads dim]: both rotated, keys times ``k_scale``.  ``silu``:
+    every channel passes SiLU first.  ``v_out`` [T, nv] (32-bit): the columns from ``v_off`` on, through the same
+    activation."""
+    _need_cuda(proj, qk, v_out)
     check(library().mf_retention_prepare(proj.data_ptr(), dtype_code(proj), proj.shape[0], proj.shape[1], n_heads, dim,
                                          rot, k_scale, positions.data_ptr(), _ptr(inv_f), _ptr(inv_d), qk.data_ptr(),
+                                         int(silu), _ptr(v_out), v_off, v_out.shape[1] if v_out is not None else 0,
                                          _stream()), "retention_prepare")
 
 
@@ -309,12 +314,14 @@ def retention_recurrence(qk: torch.Tensor, v: torch.Tensor, v_ld: int, decay: to
 
 
 def retention_output(o: torch.Tensor, gate: torch.Tensor, gate_ld: int, eps: float, out: torch.Tensor, n_heads: int,
-                     vdim: int) -> None:
+                     vdim: int, weight: Optional[torch.Tensor] = None, whole: bool = False,
+                     gate_act: str = "silu") -> None:
     """``o`` [parts, T, n_heads * vdim]: the partial read-outs, summed here.  ``gate`` points at the first gate of
     the first token; rows are ``gate_ld`` elements apart."""
     _need_cuda(o, out)
     check(library().mf_retention_output(o.data_ptr(), o.shape[0], o.stride(0), gate.data_ptr(), dtype_code(out), gate_ld,
-                                        eps, out.data_ptr(), o.shape[1], n_heads, vdim, _stream()), "retention_output")
+                                        eps, out.data_ptr(), o.shape[1], n_heads, vdim, _ptr(weight), int(whole),
+                                        {"silu": 0, "sigmoid": 1}[gate_act], _stream()), "retention_output")
 
 
 def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> None:
@@ -716,38 +723,125 @@ def delta_recurrence(qkv: torch.Tensor, beta: torch.Tensor, ag: torch.Tensor, st
 
 
 def delta_output(o: torch.Tensor, gate: torch.Tensor, gate_ld: int, weight: torch.Tensor, eps: float,
-                 out: torch.Tensor, n_heads: int, vdim: int) -> None:
-    """``gate`` points at the first gate of the first token; rows are ``gate_ld`` floats apart."""
+                 out: torch.Tensor, n_heads: int, vdim: int, weight_per_head: bool = False) -> None:
+    """``gate`` points at the first gate of the first token; rows are ``gate_ld`` floats apart.  ``weight`` is
+    [vdim], shared by the heads, or with ``weight_per_head`` [n_heads * vdim]."""
     _need_cuda(o, weight, out)
     check(library().mf_delta_output(o.data_ptr(), gate.data_ptr(), gate_ld, weight.data_ptr(), eps, out.data_ptr(),
-                                    dtype_code(out), o.shape[0], n_heads, vdim, _stream()), "delta_output")
+                                    dtype_code(out), o.shape[0], n_heads, vdim, int(weight_per_head), _stream()),
+          "delta_output")
+
+
+def delta_gates_ex(decay_in: torch.Tensor, decay_ld: int, per_head: bool, kind: int, c: float,
+                   a_log: Optional[torch.Tensor], bias: Optional[torch.Tensor], gate_in: torch.Tensor, gate_ld: int,
+                   gate_act: str, ag: torch.Tensor, n_heads: int, dim: int, n_gate: int) -> None:
+    """``ag`` [T, n_heads * dim + n_gate] (32-bit): a decay per head and key channel from ``decay_in`` (one number
+    per head with ``per_head``, shared by its channels), then the gates from ``gate_in``.  ``kind`` 0:
+    ``exp(-exp(a_log_h) softplus(x + bias))``; 1: ``exp(-c sigmoid(x + bias))``.  ``gate_act``: ``"sigmoid"`` or
+    ``"silu"``.  The inputs are 32-bit, first element of the first token, rows ``*_ld`` floats apart."""
+    _need_cuda(ag, a_log, bias)       # the inputs may be column ranges of wider rows
+    check(library().mf_delta_gates_ex(decay_in.data_ptr(), decay_ld, int(per_head), kind, c, _ptr(a_log), _ptr(bias),
+                                      gate_in.data_ptr(), gate_ld, {"sigmoid": 0, "silu": 1}[gate_act], ag.data_ptr(),
+                                      ag.shape[0], n_heads, dim, n_gate, _stream()), "delta_gates")
+
+
+def gdelta_prepare(proj: torch.Tensor, a_bias: Optional[torch.Tensor], ops_out: torch.Tensor, low: torch.Tensor,
+                   low_off: int, n_heads: int, dim: int) -> None:
+    """Operands of the generalized delta rule from ``proj`` [T, r | k | v | a | ...] (32-bit): ``ops_out``
+    [T, 4 n_heads dim] gets r | k | unit k | sigmoid(a + a_bias) * unit k; ``low`` [T, rank] gets tanh of the
+    columns from ``low_off`` on."""
+    _need_cuda(proj, ops_out, low, a_bias)
+    check(library().mf_gdelta_prepare(proj.data_ptr(), proj.shape[1], _ptr(a_bias), ops_out.data_ptr(), low.data_ptr(),
+                                      dtype_code(low), low_off, low.shape[1], proj.shape[0], n_heads, dim, _stream()),
+          "gdelta_prepare")
+
+
+def gdelta_recurrence(ops_in: torch.Tensor, w: torch.Tensor, w_ld: int, v: torch.Tensor, v_ld: int,
+                      state: torch.Tensor, batch, o_out: torch.Tensor, n_heads: int, dim: int) -> None:
+    """``S <- diag(w) S - (a u)(u^T S) + k v^T; o = S^T r`` per head from the slot's state, token after token."""
+    _need_cuda(ops_in, w, state, o_out)
+    check(library().mf_gdelta_recurrence(ops_in.data_ptr(), w.data_ptr(), w_ld, v.data_ptr(), v_ld, state.data_ptr(),
+                                         state.stride(0), batch.seq_q_start.data_ptr(), batch.seq_q_len.data_ptr(),
+                                         batch.slots.data_ptr(), o_out.data_ptr(), batch.n_seqs, n_heads, dim,
+                                         _stream()), "gdelta_recurrence")
+
+
+# ---------------------------------------------------------------------------- a sublayer's input and its norm
+
+def conv_input(x: torch.Tensor, w: torch.Tensor, state: torch.Tensor, tail_off: int, batch, out: torch.Tensor) -> None:
+    """``out = x + conv(x)``: ``x`` [T, H] the 32-bit stream, ``w`` [H, taps] (32-bit), the last taps-1 rows of
+    every sequence in its slot of ``state`` from float ``tail_off`` on; they move on after they were read."""
+    _need_cuda(x, w, state, out)
+    T, H = x.shape
+    taps = w.shape[1]
+    check(library().mf_conv_input(x.data_ptr(), T, H, w.data_ptr(), taps, state.data_ptr(), state.stride(0), tail_off,
+                                  batch.seq_of_token.data_ptr(), batch.seq_q_start.data_ptr(),
+                                  batch.seq_q_len.data_ptr(), batch.slots.data_ptr(), batch.n_seqs, out.data_ptr(),
+                                  dtype_code(out), _stream()), "conv_input", launches=2 if taps > 1 else 1)
+
+
+def postnorm_add(x: torch.Tensor, y1: torch.Tensor, s1: float, y2: Optional[torch.Tensor], s2: float,
+                 weight: torch.Tensor, eps: float) -> None:
+    """``x += rms(s1 y1 + s2 y2) * weight`` on the 32-bit stream ``x`` [T, H]; ``y2`` may be None."""
+    _need_cuda(x, y1, y2, weight)
+    if y2 is not None and y2.dtype != y1.dtype:
+        raise KernelError("postnorm_add: the two branches must have one dtype")
+    check(library().mf_postnorm_add(x.data_ptr(), x.shape[0], x.shape[1], y1.data_ptr(), s1, _ptr(y2), s2,
+                                    dtype_code(y1), weight.data_ptr(), eps, _stream()), "postnorm_add")
+
+
+def qk_norm_rope(proj: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, v_dim: int, rot: int,
+                 values_from_keys: bool, eps: float, magnitude: float, bias, q_w, k_w, inv_f, inv_d, vinv_f, vinv_d,
+                 batch, block_table: torch.Tensor, page_size: int, q_out: torch.Tensor, k_pool: torch.Tensor,
+                 v_pool: torch.Tensor, write_kv: bool) -> None:
+    """Biases, the norms of queries and keys over their whole projections, the rotation (cosine and sine times
+    ``magnitude``), the values (own, optionally rotated with ``vinv_*``, or the keys as projected) and the cache
+    write."""
+    _need_cuda(proj, q_out, k_pool, v_pool, bias, q_w, k_w, inv_f, inv_d, vinv_f, vinv_d, block_table)
+    check(library().mf_qk_norm_rope(proj.data_ptr(), proj.shape[1], dtype_code(proj), dtype_code(q_out), proj.shape[0], n_heads, n_kv,
+                                    head_dim, v_dim, rot, 1 if values_from_keys else 0, eps, magnitude, _ptr(bias),
+                                    _ptr(q_w), _ptr(k_w), _ptr(inv_f), _ptr(inv_d), _ptr(vinv_f), _ptr(vinv_d),
+                                    batch.positions.data_ptr(), batch.seq_of_token.data_ptr(), block_table.data_ptr(),
+                                    block_table.shape[1], page_size, q_out.data_ptr(), k_pool.data_ptr(),
+                                    v_pool.data_ptr(), int(write_kv), _stream()), "qk_norm_rope")
+
+
+def rotate_rows(x: torch.Tensor, n_heads: int, d: int, rot: int, positions: torch.Tensor, inv_f, inv_d,
+                sign: float) -> None:
+    """The heads of every row of ``x`` [T, n_heads * d] turned in place by ``sign * position`` (half-split pairs
+    over the first ``rot`` channels)."""
+    _need_cuda(x, positions, inv_f, inv_d)
+    check(library().mf_rotate_rows(x.data_ptr(), dtype_code(x), x.shape[0], n_heads, d, rot, positions.data_ptr(),
+                                   _ptr(inv_f), _ptr(inv_d), sign, _stream()), "rotate_rows")
 
 
 # ---------------------------------------------------------------------------- mixture of experts
 
 def moe_route(z: torch.Tensor, n_groups: int, keep: int, top: int, route_scale: float, ids: torch.Tensor,
               weights: torch.Tensor, n_experts: Optional[int] = None, softmax: bool = False,
-              bias: Optional[torch.Tensor] = None) -> None:
+              bias: Optional[torch.Tensor] = None, renormalize: bool = False) -> None:
     """The router's choice from logits ``z`` [T, >= n_experts] (the first ``n_experts`` columns of every row;
     default all): scores by sigmoid or, with ``softmax``, by a softmax over the experts; ``bias`` (32-bit, one
-    per expert) is added for the choice only."""
+    per expert) is added for the choice only; ``renormalize``: the chosen weights are divided by their sum."""
     _need_cuda(z, ids, weights, bias)
     E = z.shape[1] if n_experts is None else n_experts
     check(library().mf_moe_route(z.data_ptr(), z.shape[1], z.shape[0], E, n_groups, keep, top, route_scale,
-                                 1 if softmax else 0, _ptr(bias), ids.data_ptr(), weights.data_ptr(), _stream()),
+                                 (1 if softmax else 0) | (2 if renormalize else 0), _ptr(bias), ids.data_ptr(),
+                                 weights.data_ptr(), _stream()),
           "moe_route")
 
 
 def moe_rows(x: torch.Tensor, w_gu: torch.Tensor, w_down: torch.Tensor, ids: torch.Tensor, y: torch.Tensor,
-             limit: float, alpha: float, up_offset: float = 1.0) -> None:
-    """y [T, top, moe_rows_slices(ff), H] (32-bit) = each chosen expert's output for its token, in the
+             limit: float, alpha: float, up_offset: float = 1.0, act: Optional[str] = None) -> None:
+    """``act`` (an activation without a gate): the experts are ``down(act(up x))`` and ``w_gu`` is [E, 1, ff, H].
+    y [T, top, moe_rows_slices(ff), H] (32-bit) = each chosen expert's output for its token, in the
     partial sums of the slices its columns are cut into, not yet weighted.  A choice beyond the stacked
     experts (an identity expert) writes nothing."""
     _need_cuda(x, w_gu, w_down, ids, y)
     T, H = x.shape
     check(library().mf_moe_rows(x.data_ptr(), w_gu.data_ptr(), w_down.data_ptr(), dtype_code(x), ids.data_ptr(),
                                 y.data_ptr(), T, H, w_down.shape[2], ids.shape[1], limit, alpha, up_offset,
-                                w_down.shape[0], _stream()),
+                                w_down.shape[0], -1 if act is None else activation_code(act), _stream()),
           "moe_rows")
 
 
@@ -874,13 +968,13 @@ def moe_activation(gu: torch.Tensor, act: torch.Tensor, limit: float, alpha: flo
 
 def moe_grouped_up(x: torch.Tensor, w_gu: torch.Tensor, row_token: torch.Tensor, meta: torch.Tensor,
                    tiles: torch.Tensor, act: torch.Tensor, top: int, limit: float, alpha: float,
-                   up_offset: float = 1.0) -> None:
+                   up_offset: float = 1.0, ungated: Optional[str] = None) -> None:
     _need_cuda(x, w_gu, row_token, meta, tiles, act)
     T, H = x.shape
     E, _, ff, _ = w_gu.shape
     check(library().mf_moe_grouped_up(x.data_ptr(), w_gu.data_ptr(), row_token.data_ptr(), meta.data_ptr(),
                                       tiles.data_ptr(), act.data_ptr(), T, H, ff, E, top, limit, alpha, up_offset,
-                                      _stream()),
+                                      -1 if ungated is None else activation_code(ungated), _stream()),
           "moe_grouped_up")
 
 

@@ -24,11 +24,13 @@ constexpr int RT_THREADS = RT_LANES * RT_COLS;
 constexpr int RT_CHUNK = 8;                 // tokens staged at a time
 }  // namespace
 
+// act 1: SiLU of every query and key channel before anything else.  v_out (optional): the row's `nv`
+// channels from column `v_off` on, through the same activation, in 32-bit [T, nv].
 template <typename T>
 __global__ void retention_prepare_kernel(const T* __restrict__ proj, int ld, int n_heads, int dim, int rot,
                                          float k_scale, const int* __restrict__ positions,
                                          const float* __restrict__ inv_f, const double* __restrict__ inv_d,
-                                         float* __restrict__ qk) {
+                                         float* __restrict__ qk, int act, float* __restrict__ v_out, int v_off, int nv) {
   extern __shared__ float cs[];            // [half] cos, [half] sin
   pdl_launch();
   const int t = blockIdx.x;
@@ -40,6 +42,10 @@ __global__ void retention_prepare_kernel(const T* __restrict__ proj, int ld, int
   const T* row = proj + (long long)t * ld;
   float* out = qk + (long long)t * 2 * n_heads * dim;
   const int per_head = dim - half;
+  auto rd = [&](const T* p) {
+    const float x = to_f32<T>(*p);
+    return act ? x / (1.0f + expf(-x)) : x;
+  };
   for (int idx = threadIdx.x; idx < 2 * n_heads * per_head; idx += blockDim.x) {
     const int h = idx / per_head, j = idx - h * per_head;       // heads 0..n-1: queries, n..2n-1: keys
     const T* src = row + (long long)h * dim;
@@ -47,29 +53,32 @@ __global__ void retention_prepare_kernel(const T* __restrict__ proj, int ld, int
     const float f = h >= n_heads ? k_scale : 1.0f;
     if (j < half) {
       const float c = cs[j], s = cs[half + j];
-      const float u = to_f32<T>(src[j]), v = to_f32<T>(src[j + half]);
+      const float u = rd(src + j), v = rd(src + j + half);
       dst[j] = (u * c - v * s) * f;
       dst[j + half] = (v * c + u * s) * f;
     } else {
       const int ch = rot + (j - half);
-      dst[ch] = to_f32<T>(src[ch]) * f;
+      dst[ch] = rd(src + ch) * f;
     }
   }
+  if (v_out)
+    for (int i = threadIdx.x; i < nv; i += blockDim.x) v_out[(long long)t * nv + i] = rd(row + v_off + i);
 }
 
 MF_API int mf_retention_prepare(const void* proj, int dtype, int T, int ld, int n_heads, int dim, int rot,
                                 float k_scale, const int* positions, const float* inv_f, const double* inv_d,
-                                float* qk, cudaStream_t stream) {
+                                float* qk, int act, float* v_out, int v_off, int nv, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (rot < 0 || rot > dim || (rot & 1) || (rot > 0 && !inv_f && !inv_d)) return MF_ERR_BAD_ARG;
   const size_t smem = (size_t)(rot > 0 ? rot : 1) * sizeof(float);
   mf_count(MF_K_RETENTION_PREPARE);
   if (dtype == MF_F32)
     return (int)launch_dep(retention_prepare_kernel<float>, dim3(T), dim3(256), smem, stream, (const float*)proj, ld,
-                           n_heads, dim, rot, k_scale, positions, inv_f, inv_d, qk);
+                           n_heads, dim, rot, k_scale, positions, inv_f, inv_d, qk, act, v_out, v_off, nv);
   if (dtype == MF_BF16)
     return (int)launch_dep(retention_prepare_kernel<__nv_bfloat16>, dim3(T), dim3(256), smem, stream,
-                           (const __nv_bfloat16*)proj, ld, n_heads, dim, rot, k_scale, positions, inv_f, inv_d, qk);
+                           (const __nv_bfloat16*)proj, ld, n_heads, dim, rot, k_scale, positions, inv_f, inv_d, qk,
+                           act, v_out, v_off, nv);
   return MF_ERR_BAD_DTYPE;
 }
 
@@ -316,51 +325,68 @@ MF_API int mf_retention_recurrence(const float* qk, const void* v, int v_dtype, 
   return MF_ERR_BAD_DTYPE;
 }
 
-// out[t, h, :] = o[t, h, :] / sqrt(mean(o[t, h, :]^2) + eps) * silu(gate[t, h, :]); a warp per (token, head)
+// out[t, h, :] = o[t, h, :] / sqrt(mean(o[t, h, :]^2) + eps) * silu(gate[t, h, :]); a warp per (token, head).
+// whole: one root mean square over all heads of the token instead of one per head.  weight (optional):
+// [n_heads * vdim], multiplied in.  gate_act 1: the gate passes a sigmoid instead of SiLU.
 template <typename T>
 __global__ void retention_output_kernel(const float* __restrict__ o, int n_parts, long long part_stride,
                                         const T* __restrict__ gate, long long gate_ld, float eps, T* __restrict__ out,
-                                        int n_heads, int vdim) {
+                                        int n_heads, int vdim, const float* __restrict__ weight, int whole,
+                                        int gate_act) {
+  extern __shared__ float ro_ss[];      // [n_heads] sums of squares
   pdl_launch();
   pdl_wait();
   const int t = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  auto read = [&](const float* orow, int d) {
+    // the read-out is the sum of the row groups' partial read-outs, added in their order
+    float v = orow[d];
+    for (int p = 1; p < n_parts; p++) v += orow[p * part_stride + d];
+    return v;
+  };
   for (int h = warp; h < n_heads; h += nw) {
     const float* orow = o + ((long long)t * n_heads + h) * vdim;
-    const T* grow = gate + (long long)t * gate_ld + (long long)h * vdim;
-    // the read-out is the sum of the row groups' partial read-outs, added in their order
-    auto read = [&](int d) {
-      float v = orow[d];
-      for (int p = 1; p < n_parts; p++) v += orow[p * part_stride + d];
-      return v;
-    };
     float ss = 0.f;
     for (int d = lane; d < vdim; d += 32) {
-      const float v = read(d);
+      const float v = read(orow, d);
       ss += v * v;
     }
     ss = warp_sum(ss);
-    const float inv = 1.0f / sqrtf(ss / (float)vdim + eps);
+    if (lane == 0) ro_ss[h] = ss;
+  }
+  __syncthreads();
+  float all = 0.f;
+  if (whole)
+    for (int h = 0; h < n_heads; h++) all += ro_ss[h];
+  for (int h = warp; h < n_heads; h += nw) {
+    const float* orow = o + ((long long)t * n_heads + h) * vdim;
+    const T* grow = gate + (long long)t * gate_ld + (long long)h * vdim;
+    const float inv = whole ? 1.0f / sqrtf(all / (float)(n_heads * vdim) + eps) : 1.0f / sqrtf(ro_ss[h] / (float)vdim + eps);
     T* dst = out + ((long long)t * n_heads + h) * vdim;
     for (int d = lane; d < vdim; d += 32) {
       const float g = to_f32<T>(grow[d]);
-      dst[d] = from_f32<T>(read(d) * inv * (g / (1.0f + expf(-g))));
+      const float sg = 1.0f / (1.0f + expf(-g));
+      const float w = weight ? weight[h * vdim + d] : 1.0f;
+      dst[d] = from_f32<T>(read(orow, d) * inv * w * (gate_act ? sg : g * sg));
     }
   }
 }
 
 MF_API int mf_retention_output(const float* o, int n_parts, long long part_stride, const void* gate, int dtype,
                                long long gate_ld, float eps, void* out, int T, int n_heads, int vdim,
-                               cudaStream_t stream) {
+                               const float* weight, int whole, int gate_act, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (n_parts < 1) return MF_ERR_BAD_ARG;
   mf_count(MF_K_RETENTION_OUTPUT);
   const int threads = n_heads >= 8 ? 256 : 32 * (n_heads > 0 ? n_heads : 1);
+  const size_t smem = (size_t)(n_heads > 0 ? n_heads : 1) * sizeof(float);
+  if (smem > 48 * 1024) return MF_ERR_BAD_ARG;
   if (dtype == MF_F32)
-    return (int)launch_dep(retention_output_kernel<float>, dim3(T), dim3(threads), 0, stream, o, n_parts, part_stride,
-                           (const float*)gate, gate_ld, eps, (float*)out, n_heads, vdim);
+    return (int)launch_dep(retention_output_kernel<float>, dim3(T), dim3(threads), smem, stream, o, n_parts, part_stride,
+                           (const float*)gate, gate_ld, eps, (float*)out, n_heads, vdim, weight, whole, gate_act);
   if (dtype == MF_BF16)
-    return (int)launch_dep(retention_output_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream, o, n_parts,
-                           part_stride, (const __nv_bfloat16*)gate, gate_ld, eps, (__nv_bfloat16*)out, n_heads, vdim);
+    return (int)launch_dep(retention_output_kernel<__nv_bfloat16>, dim3(T), dim3(threads), smem, stream, o, n_parts,
+                           part_stride, (const __nv_bfloat16*)gate, gate_ld, eps, (__nv_bfloat16*)out, n_heads, vdim,
+                           weight, whole, gate_act);
   return MF_ERR_BAD_DTYPE;
 }

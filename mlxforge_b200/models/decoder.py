@@ -84,11 +84,27 @@ class DecoderModel:
         paged: List[list] = []     # [need, lanes]
         state: List[list] = []
         item_lane: List[Optional[tuple]] = []
+
+        def place(need, layer: int) -> tuple:
+            """The group and lane of one need: a lane more in the group of equal needs, or a new group."""
+            if isinstance(need, PagedKV):
+                groups, kind = paged, "paged"
+            elif isinstance(need, FixedState):
+                groups, kind = state, "state"
+            else:
+                raise TypeError(f"mixer of layer {layer} declares an unknown cache need {need!r}")
+            for g, (n, lanes) in enumerate(groups):
+                if n == need:
+                    groups[g][1] += 1
+                    return (kind, g, lanes)
+            groups.append([need, 1])
+            return (kind, len(groups) - 1, 0)
+
         for i, item in enumerate(self.spec.schedule):
             if item.cache_of is not None:
                 src = item_lane[item.cache_of]
                 need = self.blocks[item.layer].cache_need()
-                if src is None or src[0] != "paged":
+                if src is None or isinstance(src[0], tuple) or src[0] != "paged":
                     raise ValueError(f"schedule item {i} reads the cache of item {item.cache_of}, which has none to share")
                 src_need = paged[src[1]][0]
                 if not isinstance(need, PagedKV) or (need.n_kv_heads, need.head_dim, need.value_dim) != (
@@ -97,28 +113,11 @@ class DecoderModel:
                 item_lane.append(src)
                 continue
             need = self.blocks[item.layer].cache_need()
-            if need is None:
-                item_lane.append(None)
-            elif isinstance(need, PagedKV):
-                for g, (n, lanes) in enumerate(paged):
-                    if n == need:
-                        item_lane.append(("paged", g, lanes))
-                        paged[g][1] += 1
-                        break
-                else:
-                    paged.append([need, 1])
-                    item_lane.append(("paged", len(paged) - 1, 0))
-            elif isinstance(need, FixedState):
-                for g, (n, lanes) in enumerate(state):
-                    if n == need:
-                        item_lane.append(("state", g, lanes))
-                        state[g][1] += 1
-                        break
-                else:
-                    state.append([need, 1])
-                    item_lane.append(("state", len(state) - 1, 0))
+            if isinstance(need, tuple):
+                # several needs: the item's lanes are a tuple in the order of the needs
+                item_lane.append(tuple(place(n, item.layer) for n in need))
             else:
-                raise TypeError(f"mixer of layer {item.layer} declares an unknown cache need {need!r}")
+                item_lane.append(None if need is None else place(need, item.layer))
         return CacheLayout(tuple(GroupLayout(n, l) for n, l in paged), tuple(GroupLayout(n, l) for n, l in state),
                            tuple(item_lane))
 

@@ -242,3 +242,155 @@ class SinkAttention(AttentionMixer):
         options_paged_attention(self.rt, batch, q, cache, o, self.n_heads, self.scale, self.window, self.keep_first,
                                 self.sink, gate, proj.shape[1])
         return self.rt.linear(o, self.w_o, self.rt.buffer("sattn.delta", (o.shape[0], self.hidden)))
+
+
+_NORMED_NAMES = {"q": "q", "k": "k", "v": "v", "o": "o", "q_bias": "q.b", "k_bias": "k.b", "q_norm": "q.norm",
+                 "k_norm": "k.norm"}
+
+
+@register_mixer("normed_attention")
+class NormedAttention(Mixer):
+    """Grouped-query attention whose queries and keys are normalised over their WHOLE projections (one root
+    mean square over all heads' rows of q, one over k's, each with a plain weight of that size) before they
+    are rotated.  Every option is a parameter:
+
+    * ``bias``: q and k projections have biases (added in 32-bit before the norm);
+    * ``qk_norm``: ``"whole"`` or None;
+    * ``rotary``: ``{"dims", "base", "scaling"}`` - half-split pairs over the first ``dims`` channels of a head;
+      ``scaling`` None, ``{"factor"}`` (every frequency divided by it) or ``{"factor", "original", "fast",
+      "slow"}`` (the stretched table, cosine and sine times ``0.1 ln(factor) + 1``);
+    * ``values``: ``"own"`` (a value projection, ``v_head_dim`` wide per head) or ``"keys"`` (the keys as
+      projected, with their bias, before norm and rotation);
+    * ``rotate_values``: the value of position j is turned by j over all its channels (half-split pairs, pair m
+      by ``j * base^(-2m/v_head_dim)``, no scaling) before it is cached, and a head's output at position i is
+      turned back by i;
+    * ``softmax_scale``, ``softcap`` (``cap * tanh(score / cap)``), ``window`` (0: causal);
+    * ``out_f32``: the output projection is written in 32-bit."""
+
+    graph_safe = True
+
+    def __init__(self, params, prefix, runtime):
+        super().__init__(params, prefix, runtime)
+        p = params
+        self.hidden = int(p["hidden_size"])
+        self.n_heads = int(p["n_heads"])
+        self.n_kv = int(p["n_kv_heads"])
+        self.hd = int(p["head_dim"])
+        self.vd = int(p.get("v_head_dim") or self.hd)
+        self.scale = float(p["softmax_scale"])
+        self.softcap = float(p.get("softcap") or 0.0)
+        self.window = int(p.get("window", 0) or 0)
+        self.values = str(p.get("values", "own"))
+        self.bias = bool(p.get("bias", False))
+        self.qk_norm = p.get("qk_norm")
+        self.eps = float(p.get("eps", 1e-6))
+        self.rotate_values = bool(p.get("rotate_values", False))
+        self.out_f32 = bool(p.get("out_f32", False))
+        self.names = dict(_NORMED_NAMES, **(p.get("names") or {}))
+        if self.values not in ("own", "keys"):
+            raise ValueError(f"normed_attention: values must be 'own' or 'keys', got '{self.values}'")
+        if self.qk_norm not in (None, "whole"):
+            raise ValueError(f"normed_attention: qk_norm must be 'whole' or None, got '{self.qk_norm}'")
+        if self.n_kv <= 0 or self.n_heads % self.n_kv:
+            raise ValueError("n_heads must be a multiple of n_kv_heads")
+        if self.values == "keys" and self.vd != self.hd:
+            raise ValueError("normed_attention: values that are the keys have the keys' size")
+        if self.rotate_values and self.vd % 2:
+            raise ValueError("normed_attention: rotated values need an even v_head_dim")
+        from .rope import inverse_wavelengths, stretched_inverse_wavelengths
+        rot = p.get("rotary") or {}
+        self.rot = int(rot.get("dims", 0) or 0)
+        if self.rot % 2 or self.rot > self.hd:
+            raise ValueError(f"normed_attention: rotary dims {self.rot} must be even and at most head_dim")
+        base, sc = float(rot.get("base", 10000.0)), rot.get("scaling") or None
+        self.magnitude = 1.0
+        if sc and "original" in sc:
+            inv_f, inv_d, self.magnitude = stretched_inverse_wavelengths(self.rot, base, sc, runtime.device)
+        else:
+            inv_f, inv_d = inverse_wavelengths(self.rot, base, runtime.device)
+            if sc:
+                inv_d = inv_d / float(sc["factor"])
+                inv_f = inv_d.to(torch.float32)
+        self.inv_f, self.inv_d = inv_f, (inv_d if runtime.precise else None)
+        self.vinv_f = self.vinv_d = None
+        if self.rotate_values:
+            vf, vd = inverse_wavelengths(self.vd, base, runtime.device)
+            self.vinv_f, self.vinv_d = vf, (vd if runtime.precise else None)
+        self.w_in = self.w_o = self.b_in = self.q_w = self.k_w = None
+
+    def _n(self, role: str) -> str:
+        return self.prefix + self.names[role]
+
+    def _roles(self):
+        return ("q", "k") + (("v",) if self.values == "own" else ())
+
+    def tensor_specs(self) -> Dict[str, TensorSpec]:
+        nq, nk, nv = self.n_heads * self.hd, self.n_kv * self.hd, self.n_kv * self.vd
+        rows = {"q": nq, "k": nk, "v": nv}
+        specs = {self._n(r): TensorSpec((rows[r], self.hidden)) for r in self._roles()}
+        specs[self._n("o")] = TensorSpec((self.hidden, self.n_heads * self.vd))
+        if self.bias:
+            specs[self._n("q_bias")] = TensorSpec((nq,), role="vector")
+            specs[self._n("k_bias")] = TensorSpec((nk,), role="vector")
+        if self.qk_norm:
+            specs[self._n("q_norm")] = TensorSpec((nq,), role="vector")
+            specs[self._n("k_norm")] = TensorSpec((nk,), role="vector")
+        return specs
+
+    def bind(self, tensors) -> None:
+        dt, f32 = self.rt.dtype, torch.float32
+        self.w_in = torch.cat([tensors[self._n(r)].to(dt) for r in self._roles()], dim=0).contiguous()
+        self.w_o = tensors[self._n("o")].to(dt).contiguous()
+        if self.bias:
+            b = [tensors[self._n("q_bias")].to(f32), tensors[self._n("k_bias")].to(f32)]
+            if self.values == "own":
+                b.append(torch.zeros(self.n_kv * self.vd, dtype=f32, device=b[0].device))
+            self.b_in = torch.cat(b).contiguous()
+        if self.qk_norm:
+            self.q_w = tensors[self._n("q_norm")].to(f32).contiguous()
+            self.k_w = tensors[self._n("k_norm")].to(f32).contiguous()
+
+    def weight_bytes(self) -> int:
+        return (self.w_in.numel() + self.w_o.numel()) * self.w_in.element_size()
+
+    def cache_need(self):
+        return PagedKV(self.n_kv, self.hd, self.window, v_head_dim=0 if self.vd == self.hd else self.vd)
+
+    def forward(self, x, batch, cache, writes_cache: bool = True):
+        rt, T = self.rt, x.shape[0]
+        # the projections feed 32-bit norms: they are written in 32-bit and rounded once, after norm and rotation
+        proj = rt.linear(x, self.w_in, rt.buffer("nattn.in", (T, self.w_in.shape[0]), torch.float32))
+        q = rt.buffer("nattn.q", (T, self.n_heads * self.hd))
+        table = batch.block_table(cache.group)
+        ops.qk_norm_rope(proj, self.n_heads, self.n_kv, self.hd, self.vd, self.rot, self.values == "keys", self.eps,
+                         self.magnitude, self.b_in, self.q_w, self.k_w, self.inv_f, self.inv_d, self.vinv_f, self.vinv_d,
+                         batch, table, cache.page_size, q, cache.k, cache.v, writes_cache)
+        o = rt.buffer("nattn.o", (T, self.n_heads * self.vd))
+        softcap_attention(rt, batch, q, cache, o, self.n_heads, self.scale, self.window, self.softcap)
+        if self.rotate_values:
+            ops.rotate_rows(o, self.n_heads, self.vd, self.vd, batch.positions, self.vinv_f, self.vinv_d, -1.0)
+        return rt.linear(o, self.w_o, rt.buffer("nattn.delta", (T, self.hidden), torch.float32 if self.out_f32 else None))
+
+
+def softcap_attention(rt, batch, q, lane, out, n_heads: int, scale: float, window: int, softcap: float) -> None:
+    """Attention over ``lane`` (values of their own width in a pool of their own) with a window and a soft cap
+    on the scaled scores; kernels chosen as in ``options_paged_attention``."""
+    need = lane.need
+    table = batch.block_table(lane.group)
+    vd = need.value_dim
+    if q.dtype != torch.bfloat16 or not ops.attention_tc_ok(need.head_dim, vd, lane.page_size):
+        ops.attention_generic_ex(q, lane.k, lane.v, out, batch.positions, batch.seq_of_token, table, lane.page_size,
+                                 n_heads, need.n_kv_heads, need.head_dim, scale, window, vd, vd, 0, None, None, 0,
+                                 softcap)
+        return
+    nd = batch.n_decode
+    if nd > 0:
+        n_o, n_ml = ops.attention_decode_scratch(nd, n_heads, need.head_dim, batch.max_ctx, window)
+        ops.attention_decode_ex(q[:nd], lane.k, lane.v, out[:nd], rt.buffer("attn.part_o", (n_o,), torch.float32),
+                                rt.buffer("attn.part_ml", (n_ml,), torch.float32), batch.positions[:nd],
+                                batch.seq_of_token[:nd], table, lane.page_size, n_heads, need.n_kv_heads,
+                                need.head_dim, scale, window, batch.max_ctx, vd, False, 0, None, None, 0, softcap)
+    if nd < batch.n_tokens:
+        ops.attention_prefill_ex(q, lane.k, lane.v, out, batch.seq_q_start[nd:], batch.seq_q_len[nd:],
+                                 batch.seq_ctx_len[nd:], nd, max(batch.q_len[nd:]), table, lane.page_size, n_heads,
+                                 need.n_kv_heads, need.head_dim, scale, window, vd, False, 0, None, None, 0, softcap)

@@ -143,7 +143,27 @@ class FixedState:
     dtype: str = "float32"
 
 
-CacheNeed = Union[PagedKV, FixedState, None]
+# What a layer keeps per request: nothing, one need, or several (a tuple, e.g. the pages of an
+# attention branch, the state of a recurrent branch beside it and the tails of a convolution on the
+# layer's input).  A layer with several gets its lanes as a tuple in the same order.
+CacheNeed = Union[PagedKV, FixedState, None, Tuple[Union[PagedKV, FixedState], ...]]
+
+
+def flatten_needs(*needs) -> tuple:
+    """The needs of several parts as one flat tuple, those without a need left out."""
+    out = []
+    for n in needs:
+        if n is None:
+            continue
+        if isinstance(n, tuple):
+            out.extend(flatten_needs(*n))
+        else:
+            out.append(n)
+    return tuple(out)
+
+
+def count_needs(need) -> int:
+    return len(flatten_needs(need))
 
 
 @dataclass(frozen=True)
@@ -153,6 +173,18 @@ class DeltaPair:
 
     first: Any = None
     second: Any = None
+
+
+@dataclass(frozen=True)
+class ScaledPair:
+    """The outputs of two branches that ran side by side on one input, with the weights of their sum:
+    ``first_scale * first + second_scale * second``.  The sum is formed in 32-bit by whoever takes it
+    (a norm on the sublayer's output does)."""
+
+    first: Any
+    first_scale: float
+    second: Any
+    second_scale: float
 
 
 # --------------------------------------------------------------------------- interfaces
@@ -274,7 +306,8 @@ class Block:
         return list(self.by_role.values())
 
     def cache_need(self) -> CacheNeed:
-        """What this layer keeps per request: its mixer's need."""
+        """What this layer keeps per request: its mixer's need (an arrangement with state of its own
+        adds it and hands a tuple on)."""
         return self.mixer.cache_need() if self.mixer is not None else None
 
     def forward(self, residual, pending, batch, cache, writes_cache: bool = True):

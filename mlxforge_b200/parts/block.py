@@ -7,7 +7,8 @@ previous block's last delta as ``pending`` and hands its own on.
 """
 from __future__ import annotations
 
-from .base import Block, DeltaPair, register_block
+from ..csrc import ops
+from .base import Block, DeltaPair, FixedState, flatten_needs, count_needs, register_block
 
 
 @register_block("prenorm")
@@ -100,3 +101,56 @@ class ParallelSharedNormBlock(Block):
         d1 = self.mixer.forward(x, batch, cache, writes_cache)
         d2 = self.feed_forward.forward(x, batch) if self.feed_forward is not None else None
         return residual, DeltaPair(d1, d2)
+
+
+@register_block("postnorm_conv")
+class PostNormConvBlock(Block):
+    """The norms sit on the sublayers' OUTPUTS and the sublayers read the stream itself through a short
+    convolution: ``x += norm1(mixer(c1(x)))``, then (if the layer has a feed-forward)
+    ``x += norm2(feed_forward(c2(x)))``, with ``c(x) = x + conv(x)`` (the ``conv_read`` connections in the
+    roles ``mixer_connection`` and ``feed_forward_connection``; a layer without one reads the stream's
+    rounding).  The norms must have ``post_add`` (``rmsnorm`` has).  A mixer may hand back a
+    ``ScaledPair`` (two branches side by side): the norm takes their weighted sum.
+
+    The layer's state is its mixer's and, behind it, one ``FixedState`` with the convolutions' last rows
+    (the mixer's connection first)."""
+
+    roles = ("mixer", "mixer_norm")
+
+    def __init__(self, by_role, runtime):
+        super().__init__(by_role, runtime)
+        if self.feed_forward is not None and self.feed_forward_norm is None:
+            raise ValueError("postnorm_conv: a feed-forward needs a feed_forward_norm")
+        self.mixer_connection = self.by_role.get("mixer_connection")
+        self.feed_forward_connection = self.by_role.get("feed_forward_connection") if self.feed_forward is not None else None
+        self.n_mixer_needs = count_needs(self.mixer.cache_need())
+        self.conv_floats = sum(c.state_floats for c in (self.mixer_connection, self.feed_forward_connection)
+                               if c is not None)
+
+    def cache_need(self):
+        own = FixedState((self.conv_floats,), tag="conv_read") if self.conv_floats else None
+        needs = flatten_needs(self.mixer.cache_need(), own)
+        return needs if len(needs) != 1 else needs[0]
+
+    def _read(self, connection, residual, batch, conv_lane, offset, name):
+        if connection is None:
+            h = self.rt.buffer(name, tuple(residual.shape))
+            h.copy_(residual)
+            return h
+        return connection.read(residual, batch, conv_lane.tensor if conv_lane is not None else residual, offset, name)
+
+    def forward(self, residual, pending, batch, cache, writes_cache: bool = True):
+        for d in ((pending.first, pending.second) if isinstance(pending, DeltaPair) else (pending,)):
+            if d is not None:
+                ops.residual_add(residual, d)
+        lanes = cache if isinstance(cache, tuple) else (() if cache is None else (cache,))
+        n = self.n_mixer_needs
+        mixer_cache = None if n == 0 else (lanes[0] if n == 1 else lanes[:n])
+        conv_lane = lanes[n] if len(lanes) > n else None
+        h = self._read(self.mixer_connection, residual, batch, conv_lane, 0, "block.read1")
+        self.mixer_norm.post_add(residual, self.mixer.forward(h, batch, mixer_cache, writes_cache))
+        if self.feed_forward is not None:
+            off = self.mixer_connection.state_floats if self.mixer_connection is not None else 0
+            h = self._read(self.feed_forward_connection, residual, batch, conv_lane, off, "block.read2")
+            self.feed_forward_norm.post_add(residual, self.feed_forward.forward(h, batch))
+        return residual, None

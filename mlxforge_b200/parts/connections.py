@@ -9,6 +9,11 @@ written back as ``x_t <- sum_s mix[s, t] x_s + out[t] y`` (all ``t`` at once fro
 The write-back is not done by the connection: it hands a ``StreamWrite`` on as the layer's pending
 delta, and the norm of the next sublayer (``group_rmsnorm``) applies it in the kernel that also
 reads and normalises, as the single stream's add is fused into the next RMSNorm.
+
+``conv_read`` is a connection on the reading side alone: the sublayer reads the stream itself plus a
+short causal convolution of it over time, per channel (``h_t = x_t + sum_j w[:, j] x_(t-taps+1+j)``,
+zeros before the sequence's start).  The last ``taps - 1`` rows it has read belong to the request's
+state; the arrangement gives it a place in a state slot.
 """
 from __future__ import annotations
 
@@ -17,6 +22,7 @@ from typing import Any, Dict, Optional
 
 import torch
 
+from ..csrc import ops
 from .base import Connection, TensorSpec, register_connection
 
 
@@ -59,3 +65,41 @@ class HyperConnection(Connection):
 
     def write(self, delta, bias=None) -> StreamWrite:
         return StreamWrite(delta, bias, self.w_mix, self.w_out)
+
+
+@register_connection("conv_read")
+class ConvRead(Connection):
+    """``read(x)`` = ``x + conv(x)`` with the weight ``tensor`` [size, taps] (no bias), in 32-bit on the
+    32-bit stream, rounded once to the compute dtype."""
+
+    graph_safe = True
+
+    def __init__(self, params, prefix, runtime):
+        super().__init__(params, prefix, runtime)
+        self.size = int(params["size"])
+        self.taps = int(params["taps"])
+        self.name = self.prefix + str(params.get("tensor", "conv"))
+        if self.taps < 1:
+            raise ValueError(f"conv_read: {self.taps} taps (at least 1)")
+        self.weight = None
+
+    @property
+    def state_floats(self) -> int:
+        """32-bit numbers of a request's state: the last taps - 1 rows of the stream."""
+        return (self.taps - 1) * self.size
+
+    def tensor_specs(self) -> Dict[str, TensorSpec]:
+        return {self.name: TensorSpec((self.size, self.taps), role="vector")}
+
+    def bind(self, tensors) -> None:
+        self.weight = tensors[self.name].to(torch.float32).contiguous()
+
+    def weight_bytes(self) -> int:
+        return self.size * self.taps * 4
+
+    def read(self, x, batch, state, offset: int, name: str = "conv.read"):
+        """``x`` [T, size] the 32-bit stream; ``state`` [slots, floats] with this connection's rows from
+        ``offset`` on.  Returns [T, size] in the compute dtype; the slots' rows move on."""
+        out = self.rt.buffer(name, (x.shape[0], self.size))
+        ops.conv_input(x, self.weight, state, offset, batch, out)
+        return out

@@ -12,6 +12,9 @@ tensor with one number per router output that steers the choice and nothing else
 
 (no ``limit``, ``alpha`` 1 and ``up_offset`` 0 make it ``Wd (silu(Wg x) * (Wu x))``).
 
+``renormalize``: the chosen experts' weights are divided by their sum (+ 1e-20).  ``expert_act`` (``"relu2"``,
+``"silu"``, ``"gelu_tanh"``): the experts have no gate, ``y = Wd_e act(Wu_e x)``, and no ``gate`` tensors.
+
 ``n_identity`` further router outputs, after the experts', stand for experts without matrices that return
 their input: a token that chooses one gets ``weight * x``.  ``shared`` (a feed-forward part's spec) is a
 branch every token takes; it is added times ``sigmoid(w_sg . x)`` where ``shared_gate`` names that row
@@ -60,6 +63,10 @@ class RoutedExperts(FeedForward):
         self.limit = float(p["limit"]) if p.get("limit") is not None else math.inf
         self.alpha = float(p.get("alpha", 1.702))
         self.up_offset = float(p.get("up_offset", 1.0))
+        self.renormalize = bool(p.get("renormalize", False))
+        self.expert_act = p.get("expert_act")
+        if self.expert_act is not None:
+            ops.activation_code(self.expert_act)
         self.choice_bias_name = p.get("choice_bias")
         self.shared_gate_name = p.get("shared_gate")
         self.names = dict(_NAMES, **(p.get("names") or {}))
@@ -93,7 +100,8 @@ class RoutedExperts(FeedForward):
     def tensor_specs(self) -> Dict[str, TensorSpec]:
         specs = {self.prefix + self.names["router"]: TensorSpec((self.n_outputs, self.hidden))}
         for e in range(self.n_experts):
-            specs[self._e(e, "gate")] = TensorSpec((self.ff, self.hidden))
+            if self.expert_act is None:
+                specs[self._e(e, "gate")] = TensorSpec((self.ff, self.hidden))
             specs[self._e(e, "up")] = TensorSpec((self.ff, self.hidden))
             specs[self._e(e, "down")] = TensorSpec((self.hidden, self.ff))
         if self.choice_bias_name:
@@ -110,12 +118,13 @@ class RoutedExperts(FeedForward):
         if self.shared_gate_name:        # the shared branch's gate logit is one more column of the router's product
             rows.append(tensors[self.prefix + self.shared_gate_name].to(dt).view(1, self.hidden))
         self.w_router = torch.cat(rows, dim=0).contiguous()
+        first = ("gate", "up") if self.expert_act is None else ("up",)
         if self.n_experts:
-            self.w_gu = torch.stack([torch.stack([tensors[self._e(e, "gate")].to(dt), tensors[self._e(e, "up")].to(dt)])
-                                     for e in range(self.n_experts)]).contiguous()           # [E, 2, ff, H]
+            self.w_gu = torch.stack([torch.stack([tensors[self._e(e, r)].to(dt) for r in first])
+                                     for e in range(self.n_experts)]).contiguous()     # [E, 2, ff, H]; [E, 1, ff, H] ungated
             self.w_down = torch.stack([tensors[self._e(e, "down")].to(dt) for e in range(self.n_experts)]).contiguous()
         else:
-            self.w_gu = torch.zeros((0, 2, self.ff, self.hidden), dtype=dt, device=self.w_router.device)
+            self.w_gu = torch.zeros((0, len(first), self.ff, self.hidden), dtype=dt, device=self.w_router.device)
             self.w_down = torch.zeros((0, self.hidden, self.ff), dtype=dt, device=self.w_router.device)
         if self.choice_bias_name:
             self.choice_bias = tensors[self.prefix + self.choice_bias_name].to(torch.float32).contiguous()
@@ -124,7 +133,7 @@ class RoutedExperts(FeedForward):
 
     def weight_bytes(self) -> int:
         # a step reads the router and, per token, `top` experts; at most all of them
-        per = 3 * self.ff * self.hidden * self.w_gu.element_size()
+        per = (3 if self.expert_act is None else 2) * self.ff * self.hidden * self.w_gu.element_size()
         shared = self.shared.weight_bytes() if self.shared is not None else 0
         return self.w_router.numel() * self.w_router.element_size() + self.n_experts * per + shared
 
@@ -136,7 +145,7 @@ class RoutedExperts(FeedForward):
         ids = self.rt.buffer("moe.ids", (T, self.top), torch.int32)
         weights = self.rt.buffer("moe.weights", (T, self.top), torch.float32)
         ops.moe_route(z, self.n_groups, self.keep, self.top, self.route_scale, ids, weights, self.n_outputs,
-                      self.scoring == "softmax", self.choice_bias)
+                      self.scoring == "softmax", self.choice_bias, self.renormalize)
         return ids, weights, z
 
     def _combine(self, y, weights, slot_of, out, slices, ids, x, z, shared):
@@ -156,7 +165,7 @@ class RoutedExperts(FeedForward):
         slices = ops.moe_rows_slices(self.ff)
         y = rt.buffer("moe.y", (T, self.top * slices, self.hidden), torch.float32)
         if self.n_experts:
-            ops.moe_rows(x, self.w_gu, self.w_down, ids, y, self.limit, self.alpha, self.up_offset)
+            ops.moe_rows(x, self.w_gu, self.w_down, ids, y, self.limit, self.alpha, self.up_offset, self.expert_act)
         self._combine(y, weights, None, out, slices, ids, x, z, shared)
         return out
 
@@ -181,12 +190,16 @@ class RoutedExperts(FeedForward):
         if self._library_grouped():
             xg = rt.buffer("moe.xg", (n, self.hidden))
             ops.moe_gather_rows(x, row_token, xg)
-            gu = torch._grouped_mm(xg, self.w_gu.view(self.n_experts, 2 * self.ff, self.hidden).transpose(1, 2), offs=ends)
-            ops.moe_activation(gu, act, self.limit, self.alpha, self.up_offset)
+            gu = torch._grouped_mm(xg, self.w_gu.view(self.n_experts, -1, self.hidden).transpose(1, 2), offs=ends)
+            if self.expert_act is None:
+                ops.moe_activation(gu, act, self.limit, self.alpha, self.up_offset)
+            else:
+                ops.unary_act(gu, act, self.expert_act)
             y = torch._grouped_mm(act, self.w_down.transpose(1, 2), offs=ends)
             self._combine(y, weights, slot_of, out, 1, ids, x, z, shared)
             return out
-        ops.moe_grouped_up(x, self.w_gu, row_token, meta, tiles, act, self.top, self.limit, self.alpha, self.up_offset)
+        ops.moe_grouped_up(x, self.w_gu, row_token, meta, tiles, act, self.top, self.limit, self.alpha, self.up_offset,
+                           self.expert_act)
         y = rt.buffer("moe.y", (n, self.hidden), torch.float32)
         ops.moe_grouped_down(act, self.w_down, meta, tiles, y, T, self.top)
         self._combine(y, weights, slot_of, out, 1, ids, x, z, shared)

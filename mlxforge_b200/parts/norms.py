@@ -2,6 +2,10 @@
 multiplying directly (src/model/decoder_model.cpp:206-208).  The sum of squares,
 the scaling and the residual sum it is fused with are 32-bit.
 
+``one_plus``: the stored weight lies around zero and ``1 + w`` multiplies.  ``scale``: a constant folded into
+the weight (a model whose logits are multiplied by a constant applies it to the final norm's rows, which
+is the same product).  ``post_add`` is the norm on a sublayer's OUTPUT: ``residual += rms(y) * w``.
+
 A layer whose branches run side by side on one residual hands on two deltas at once
 (``DeltaPair``) and wants two norms of the same sum: ``RMSNorm.pair_forward`` adds both deltas
 and applies both weights in one kernel."""
@@ -12,7 +16,7 @@ from typing import Dict
 import torch
 
 from ..csrc import ops
-from .base import DeltaPair, Norm, TensorSpec, register_norm
+from .base import DeltaPair, Norm, ScaledPair, TensorSpec, register_norm
 
 
 @register_norm("rmsnorm")
@@ -24,19 +28,34 @@ class RMSNorm(Norm):
         self.size = int(params["size"])
         self.eps = float(params["eps"])
         self.name = self.prefix + str(params.get("tensor", "weight"))
+        self.one_plus = bool(params.get("one_plus", False))
+        self.scale = float(params.get("scale", 1.0))
         self.weight = None
 
     def tensor_specs(self) -> Dict[str, TensorSpec]:
         return {self.name: TensorSpec((self.size,), role="vector")}
 
     def bind(self, tensors) -> None:
-        self.weight = tensors[self.name].to(torch.float32).contiguous()
+        w = tensors[self.name].to(torch.float32)
+        if self.one_plus:
+            w = w + 1.0
+        if self.scale != 1.0:
+            w = w * self.scale
+        self.weight = w.contiguous()
 
     def weight_bytes(self) -> int:
         return self.size * 4
 
     def forward(self, x, out=None):
         return self.add_forward(x, None, out)
+
+    def post_add(self, residual, y) -> None:
+        """``residual += rms(y) * weight`` in 32-bit, in place; ``y`` [T, size] is a sublayer's output (32-bit or
+        the compute dtype) or a ``ScaledPair`` of two branches' outputs, whose weighted sum is normalised."""
+        if isinstance(y, ScaledPair):
+            ops.postnorm_add(residual, y.first, y.first_scale, y.second, y.second_scale, self.weight, self.eps)
+        else:
+            ops.postnorm_add(residual, y, 1.0, None, 0.0, self.weight, self.eps)
 
     def add_forward(self, residual, delta, out=None, rows=None):
         n = residual.shape[0] if rows is None else rows.shape[0]

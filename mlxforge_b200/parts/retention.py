@@ -11,6 +11,12 @@ projections of the input; q and k are rotated by position (the ``rotary`` encodi
 Every head's read-out is divided by its root mean square over ``v_head_dim`` (``eps``, no weight),
 the heads are concatenated, multiplied by ``silu(W_g x)`` and projected by ``W_o``.
 
+Options, each a parameter: ``activation: "silu"`` passes q, k and v through SiLU first ("lightning" attention
+is this with ``rotary_dim`` 0 and ``key_scale`` 1); ``output_norm: "whole"`` divides the concatenated heads by
+ONE root mean square over all of them instead of one per head; ``norm_weight`` names a plain weight
+[n_heads * v_head_dim] that multiplies the normalised read-out; ``gate_act: "sigmoid"`` replaces the gate's
+SiLU; ``out_f32`` writes the output projection in 32-bit.
+
 The request's slot keeps ``S`` of every head, so a step goes on from where the step before ended,
 however the prompt was cut.  All projections that read the mixer's input are one product;
 everything after them is 32-bit.  ``names`` maps the tensors' roles to their names.
@@ -44,6 +50,16 @@ class Retention(Mixer):
         self.decay_host = [float(d) for d in p["decay"]]
         self.k_scale = float(p.get("key_scale", self.dim ** -0.5))
         self.names = dict(_NAMES, **(p.get("names") or {}))
+        self.activation = p.get("activation")
+        self.output_norm = str(p.get("output_norm", "head"))
+        self.norm_weight_name = p.get("norm_weight")
+        self.gate_act = str(p.get("gate_act", "silu"))
+        self.out_f32 = bool(p.get("out_f32", False))
+        if self.activation not in (None, "silu"):
+            raise ValueError(f"retention: activation must be 'silu' or None, got '{self.activation}'")
+        if self.output_norm not in ("head", "whole") or self.gate_act not in ("silu", "sigmoid"):
+            raise ValueError("retention: output_norm is 'head' or 'whole', gate_act 'silu' or 'sigmoid'")
+        self.norm_w = None
         if len(self.decay_host) != self.n_heads:
             raise ValueError(f"retention: {len(self.decay_host)} decays for {self.n_heads} heads")
         if self.rot % 2 or self.rot > self.dim:
@@ -60,14 +76,19 @@ class Retention(Mixer):
 
     def tensor_specs(self) -> Dict[str, TensorSpec]:
         nqk, nv, H = self.n_heads * self.dim, self.n_heads * self.vdim, self.hidden
-        return {self._n("q"): TensorSpec((nqk, H)), self._n("k"): TensorSpec((nqk, H)),
-                self._n("v"): TensorSpec((nv, H)), self._n("g"): TensorSpec((nv, H)),
-                self._n("o"): TensorSpec((H, nv))}
+        specs = {self._n("q"): TensorSpec((nqk, H)), self._n("k"): TensorSpec((nqk, H)),
+                 self._n("v"): TensorSpec((nv, H)), self._n("g"): TensorSpec((nv, H)),
+                 self._n("o"): TensorSpec((H, nv))}
+        if self.norm_weight_name:
+            specs[self.prefix + self.norm_weight_name] = TensorSpec((nv,), role="vector")
+        return specs
 
     def bind(self, tensors) -> None:
         dt = self.rt.dtype
         self.w_in = torch.cat([tensors[self._n(r)].to(dt) for r in ("q", "k", "v", "g")], dim=0).contiguous()
         self.w_o = tensors[self._n("o")].to(dt).contiguous()
+        if self.norm_weight_name:
+            self.norm_w = tensors[self.prefix + self.norm_weight_name].to(torch.float32).contiguous()
 
     def weight_bytes(self) -> int:
         return (self.w_in.numel() + self.w_o.numel()) * self.w_in.element_size()
@@ -81,10 +102,18 @@ class Retention(Mixer):
         proj = rt.linear(x, self.w_in, rt.buffer("ret.in", (T, self.w_in.shape[0])))
         ld = proj.shape[1]
         qk = rt.buffer("ret.qk", (T, 2 * nh * d), f32)
-        ops.retention_prepare(proj, nh, d, self.rot, self.k_scale, batch.positions, self.inv_f, self.inv_d, qk)
-        v = proj[:, 2 * nh * d:]
-        o = rt.buffer("ret.o", (ops.retention_parts(d, dv, v, ld), T, nh * dv), f32)
-        ops.retention_recurrence(qk, v, ld, self.decay, cache.tensor, batch, o, nh, d, dv)
+        if self.activation:
+            # the values pass the activation too: they go on in 32-bit beside the queries and keys
+            v = rt.buffer("ret.v", (T, nh * dv), f32)
+            ops.retention_prepare(proj, nh, d, self.rot, self.k_scale, batch.positions, self.inv_f, self.inv_d, qk,
+                                  True, v, 2 * nh * d)
+            v_ld = nh * dv
+        else:
+            ops.retention_prepare(proj, nh, d, self.rot, self.k_scale, batch.positions, self.inv_f, self.inv_d, qk)
+            v, v_ld = proj[:, 2 * nh * d:], ld
+        o = rt.buffer("ret.o", (ops.retention_parts(d, dv, v, v_ld), T, nh * dv), f32)
+        ops.retention_recurrence(qk, v, v_ld, self.decay, cache.tensor, batch, o, nh, d, dv)
         og = rt.buffer("ret.og", (T, nh * dv))
-        ops.retention_output(o, proj[:, 2 * nh * d + nh * dv:], ld, self.eps, og, nh, dv)
-        return rt.linear(og, self.w_o, rt.buffer("ret.delta", (T, self.hidden)))
+        ops.retention_output(o, proj[:, 2 * nh * d + nh * dv:], ld, self.eps, og, nh, dv, self.norm_w,
+                             self.output_norm == "whole", self.gate_act)
+        return rt.linear(og, self.w_o, rt.buffer("ret.delta", (T, self.hidden), f32 if self.out_f32 else None))
