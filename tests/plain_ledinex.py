@@ -40,6 +40,10 @@ def round_bf16(x):
     return u.view(np.float32).astype(np.float64)
 
 
+def round_f32(x):
+    return np.asarray(x, dtype=np.float32).astype(np.float64)
+
+
 def sigmoid(x):
     return 1.0 / (1.0 + np.exp(-x))
 
@@ -164,16 +168,18 @@ def _heads(x, n):
 def capped_attention(h, W, c, eps):
     """Left branch of ``parallel``.  ``W``: tensors by their names behind the branch's prefix."""
     T = h.shape[0]
-    H, G, d, dv = int(c["heads"]), int(c["kv_heads"]), int(c["dim"]), int(c["vdim"])
+    H, G, d, dv = int(c["heads"]), int(c.get("kv_heads") or c["heads"]), int(c["dim"]), int(c.get("vdim") or c["dim"])
     pos = np.arange(T)
     q = rms_norm(lin(h, W["q"]), W["q.norm"], eps)
     k = rms_norm(lin(h, W["k"]), W["k.norm"], eps)
     v = _heads(lin(h, W["v"]), G)
-    rot = c["rot"]
-    f, mag = frequencies_of(rot)
-    q = rotate_half(_heads(q, H), pos, int(rot["dims"]), f, mag)
-    k = rotate_half(_heads(k, G), pos, int(rot["dims"]), f, mag)
-    fv = plain_frequencies(dv, float(rot["base"]))
+    rot = c.get("rot")
+    q, k = _heads(q, H), _heads(k, G)
+    if rot:
+        f, mag = frequencies_of(rot)
+        q = rotate_half(q, pos, int(rot["dims"]), f, mag)
+        k = rotate_half(k, pos, int(rot["dims"]), f, mag)
+    fv = plain_frequencies(dv, float((rot or {}).get("base", 10000.0)))
     v = rotate_half(v, pos, dv, fv)
     o = softmax_attention(_r(q), _r(k), _r(v), float(c["scale"]), float(c.get("softcap") or 0.0),
                           int((c.get("mask") or {}).get("size") or 0))
@@ -184,17 +190,19 @@ def capped_attention(h, W, c, eps):
 def window_attention(h, W, c, eps):
     """Left branch of ``parallel_2``: the values are the keys as projected (with their bias)."""
     T = h.shape[0]
-    H, G, d = int(c["heads"]), int(c["kv_heads"]), int(c["dim"])
+    H, G, d = int(c["heads"]), int(c.get("kv_heads") or c["heads"]), int(c["dim"])
     pos = np.arange(T)
     q0 = lin(h, W["q"], W["q.b"])
     k0 = lin(h, W["k"], W["k.b"])
     v = _heads(k0, G)
     q = rms_norm(q0, W["q.norm"], eps)
     k = rms_norm(k0, W["k.norm"], eps)
-    rot = c["rot"]
-    f, mag = frequencies_of(rot)
-    q = rotate_half(_heads(q, H), pos, int(rot["dims"]), f, mag)
-    k = rotate_half(_heads(k, G), pos, int(rot["dims"]), f, mag)
+    rot = c.get("rot")
+    q, k = _heads(q, H), _heads(k, G)
+    if rot:
+        f, mag = frequencies_of(rot)
+        q = rotate_half(q, pos, int(rot["dims"]), f, mag)
+        k = rotate_half(k, pos, int(rot["dims"]), f, mag)
     o = softmax_attention(_r(q), _r(k), _r(v), float(c["scale"]), float(c.get("softcap") or 0.0),
                           int((c.get("mask") or {}).get("size") or 0))
     return lin(o.reshape(T, -1), W["o"])
@@ -284,6 +292,20 @@ def route(h, Wr, top):
     return ids, w / (w.sum(axis=1, keepdims=True) + 1e-20), s
 
 
+def choice_margins(h, Wr, top):
+    """Per token, how far the router's last chosen logit lies above the first rejected one, relative to the
+    largest logit; infinite where every expert is chosen or where the expert in question would get a
+    weight below a thousandth either way (then the choice moves nothing)."""
+    z = lin(h, Wr)
+    if z.shape[1] <= top:
+        return np.full(z.shape[0], np.inf)
+    zs = -np.sort(-z, axis=1)
+    e = np.exp(zs - zs[:, :1])
+    weight = e[:, top - 1] / e[:, :top].sum(axis=1)
+    m = (zs[:, top - 1] - zs[:, top]) / np.maximum(1.0, np.abs(z).max(axis=1))
+    return np.where(weight < 1e-3, np.inf, m)
+
+
 def mixture(h, W, c):
     """``W``: tensors by name behind the feed-forward's prefix (``router``, ``e<i>.up`` ...)."""
     ids, w, _ = route(h, W["router"], int(c["router"]["top"]))
@@ -320,25 +342,22 @@ def mixer_forward(h, layer, W, eps):
 
 def forward(config, tensors, tokens, layers_out=None, choices_out=None):
     """Logits [T, vocab] of one sequence.  ``tensors``: name -> array.  ``layers_out``: a list that gets
-    the stream after every layer.  ``choices_out``: a list that gets, per layer with experts, the margin
-    between the last chosen and the first rejected score of every token."""
+    the stream after every layer.  ``choices_out``: a list that gets, per layer with experts, the margin of
+    every token's choice (``choice_margins``)."""
     eps = float(config["norm"]["eps"])
     E = np.asarray(tensors["embed"], dtype=np.float64)
-    x = E[np.asarray(tokens)] * float(config["embedding"]["scale"])
+    x = E[np.asarray(tokens)] * float((config.get("embedding") or {}).get("scale", 1.0))
     for i, layer in enumerate(config["layers"]):
         p = f"l{i}."
-        h = _r(input_convolution(x, tensors[p + "canon1"]))
+        h = _r(input_convolution(x, tensors[p + "canon1"]))      # a file without taps has one: [width, 1]
         x = x + norm_one_plus(mixer_forward(h, layer, _sub(tensors, p + "mix."), eps), tensors[p + "norm1"], eps)
         if layer.get("mlp"):
             h = _r(input_convolution(x, tensors[p + "canon2"]))
             W = _sub(tensors, p + "mlp.")
             x = x + norm_one_plus(mixture(h, W, layer["mlp"]), tensors[p + "norm2"], eps)
             if choices_out is not None:
-                _, _, s = route(h, W["router"], 1)
-                top = int(layer["mlp"]["router"]["top"])
-                ss = -np.sort(-s, axis=1)
-                choices_out.append(ss[:, top - 1] - ss[:, top] if ss.shape[1] > top else np.full(len(tokens), np.inf))
+                choices_out.append(choice_margins(h, W["router"], int(layer["mlp"]["router"]["top"])))
         if layers_out is not None:
             layers_out.append(x.copy())
     hn = norm_one_plus(x, tensors["final.norm"], eps)
-    return lin(hn, E) * float(config["logit_scale"])
+    return lin(hn, E) * float(config.get("logit_scale", 1.0))
