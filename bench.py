@@ -515,6 +515,18 @@ def kernel_work(name, a, k, info):
     if name in ("gemm_bf16", "stream_linear"):
         x, w, out = a[0], a[1], a[2]
         return (_nbytes(x, w, out), 2.0 * x.shape[0] * w.shape[0] * w.shape[1], 0)
+    if name == "conv_input":
+        x, out = a[0], a[5]
+        return (_nbytes(x, out), 0, 0)
+    if name == "postnorm_add":
+        x, y1, y2 = a[0], a[1], a[3]
+        return (2 * _nbytes(x) + _nbytes(y1, y2), 0, 0)
+    if name == "gdelta_recurrence":
+        operands, state, o, nh, dim = a[0], a[5], a[7], a[8], a[9]
+        return (_nbytes(operands, o) + 2 * T * nh * dim * 4 + 2 * info["seqs"] * nh * dim * dim * 4, 0,
+                9.0 * T * nh * dim * dim)
+    if name in ("qk_norm_rope", "rotate_rows", "gdelta_prepare", "delta_gates_ex"):
+        return (_nbytes(*[t for t in a if hasattr(t, "numel") and t.dim() >= 2 and t.numel() < (1 << 28)]), 0, 0)
     return (0, 0, 0)
 
 
@@ -800,6 +812,113 @@ def run_rabapel(args) -> int:
     return 0
 
 
+# ---------------------------------------------------------------------------- --workload ledinex
+# The Ledinex design at sizes that resemble a real model's layers, beside the closest existing model at equal
+# size: a Notirax decoder (attention, a gated delta rule and a mixture of experts, like it) with the same width,
+# layers, vocabulary, attention heads and head size, delta heads, experts and experts' width, one residual
+# stream and one norm group.  Ledinex's layers are parallel_2, delta, parallel, delta, each with a mixture of
+# squared-rectifier experts and a shared expert.
+LEDINEX_SIZES = {
+    "s": dict(width=1024, layers=4, vocab=32768, heads=8, kv=2, dim=128, window=1024, r_heads=8, r_dim=64, rank=64,
+              l_heads=8, l_dim=64, l_vdim=128, d_heads=8, d_dim=128, conv=4, taps=3, experts=32, top=4, ff=512, shared_ff=1024,
+              context=4096),
+    "m": dict(width=2048, layers=4, vocab=32768, heads=16, kv=4, dim=128, window=2048, r_heads=16, r_dim=64, rank=64,
+              l_heads=16, l_dim=64, l_vdim=128, d_heads=16, d_dim=128, conv=4, taps=3, experts=64, top=6, ff=768, shared_ff=2048,
+              context=4096),
+}
+LEDINEX_KERNELS = ("embed", "conv_input", "postnorm_add", "qk_norm_rope", "rotate_rows", "attention_prefill_ex",
+                   "attention_decode_ex", "attention_generic_ex", "retention_prepare", "retention_recurrence",
+                   "retention_output", "gdelta_prepare", "gdelta_recurrence", "delta_gates_ex", "delta_prepare",
+                   "delta_recurrence", "delta_output", "moe_route", "moe_rows", "moe_combine", "moe_sort",
+                   "moe_grouped_up", "moe_grouped_down", "moe_gather_rows", "_grouped_mm", "unary_act", "add_rmsnorm",
+                   "stream_linear", "gemm_bf16")
+
+
+def ledinex_config(z):
+    yarn = {"factor": 8.0, "original": z["context"] // 8, "fast": 32.0, "slow": 1.0}
+    left2 = {"heads": z["heads"], "kv_heads": z["kv"], "dim": z["dim"], "vdim": z["dim"], "scale": z["dim"] ** -0.5,
+             "mask": {"size": z["window"]}, "rot": {"base": 10000.0, "dims": z["dim"] // 2, "scaling": yarn}}
+    left1 = {"heads": z["heads"], "kv_heads": z["kv"], "dim": z["dim"], "vdim": z["dim"], "scale": z["dim"] ** -0.5,
+             "softcap": 50.0, "rot": {"base": 250000.0, "dims": z["dim"], "scaling": {"factor": 4.0}}}
+    par2 = {"type": "parallel_2", "mixer": {"left": left2, "right": {"heads": z["r_heads"], "dim": z["r_dim"],
+                                                                     "decay_rank": z["rank"]},
+                                            "left_scale": 0.8, "right_scale": 0.9}}
+    par = {"type": "parallel", "mixer": {"left": left1, "right": {"heads": z["l_heads"], "dim": z["l_dim"], "vdim": z["l_vdim"],
+                                                                  "decay": [1.0 - 2.0 ** -(2 + i % 8) for i in range(z["l_heads"])]},
+                                         "left_scale": 0.8, "right_scale": 0.9}}
+    delta = {"type": "delta", "mixer": {"heads": z["d_heads"], "kv_heads": z["d_heads"], "dim": z["d_dim"], "vdim": z["d_dim"],
+                                        "conv": z["conv"]}}
+    mlp = {"kind": "moe", "expert": {"ff": z["ff"]}, "router": {"experts": z["experts"], "top": z["top"]},
+           "shared": {"ff": z["shared_ff"]}}
+    order = [par2, delta, par, delta]
+    return {"architecture": "Ledinex", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-5},
+            "embedding": {"scale": 16.0}, "logit_scale": 2.0, "canon": {"taps": z["taps"]},
+            "layers": [dict(order[i % 4], mlp=mlp) for i in range(z["layers"])]}
+
+
+def ledinex_notirax_like(z):
+    attn = {"type": "attention", "mixer": {"heads": z["heads"], "kv_heads": z["kv"], "dim": z["dim"], "vdim": z["dim"],
+                                           "scale": z["dim"] ** -0.5, "softcap": 50.0, "mask": {"size": z["window"]}}}
+    delta = {"type": "channel_delta", "mixer": {"heads": z["d_heads"], "kv_heads": z["d_heads"], "dim": z["d_dim"],
+                                                "vdim": z["d_dim"], "conv": z["conv"], "decay_rank": z["rank"],
+                                                "gate_rank": z["rank"]}}
+    mlp = {"kind": "moe", "expert": {"ff": z["ff"], "limit": 7.0}, "router": {"experts": z["experts"], "top": z["top"], "scale": 1.0}}
+    return {"architecture": "Notirax", "vocab": z["vocab"], "width": z["width"], "streams": 1,
+            "norm": {"eps": 1e-6, "groups": 1},
+            "layers": [dict(attn if i % 2 == 0 else delta, mlp=mlp) for i in range(z["layers"])]}
+
+
+def run_ledinex(args) -> int:
+    import torch
+    import mlxforge_b200 as mf
+    from mlxforge_b200.config import config_from_json
+    from mlxforge_b200.csrc import ops
+    pk = peaks()
+    out = {"workload": "ledinex", "dtype": "bf16", "peaks": pk,
+           "data": "synthetic: seeded random weights, seeded uniform token ids, random cache contents",
+           "fp32_tflops_nominal": round(FP32_TFLOPS_NOMINAL, 1), "sizes": {}}
+    sampled = []
+    for key in ([args.size] if args.size else sorted(LEDINEX_SIZES)):
+        z = LEDINEX_SIZES[key]
+        res = {"size": z}
+        for which, cfg_json, names, chunk in (("ledinex", ledinex_config(z), LEDINEX_KERNELS, 0),
+                                              ("notirax_equal_size", ledinex_notirax_like(z), NOTIRAX_KERNELS, z["window"])):
+            tmp = tempfile.mkdtemp(prefix="mlxforge_bench_")
+            try:
+                d = mf.write_random_model(os.path.join(tmp, "model"), config_from_json(cfg_json), seed=0, dtype="bfloat16")
+                engine = mf.Engine(model_spec=d, dtype="bfloat16", kv_pool_tokens=(args.batch + 2) * (z["context"] + 2048 + 64),
+                                   max_running=max(8, args.batch), token_budget=8192, prefill_chunk=2048)
+            finally:
+                shutil.rmtree(tmp, ignore_errors=True)
+            for pool in set(engine.cache._k + engine.cache._v):
+                pool.normal_(0.0, 1.0)
+            ctx = z["context"]
+            clocks = ClockSampler()
+            clocks.start()
+            t_pre = prefill_device(engine, PREFILL_TOKENS, runs=3, warmup=3)
+            sec, launches, _, _ = decode_device(engine, args.batch, ctx, args.steps, args.warmup)
+            r = {"prefill_tokens": PREFILL_TOKENS, "prefill_ms": round(t_pre * 1e3, 3),
+                 "prefill_tokens_per_s": round(PREFILL_TOKENS / t_pre, 1), "decode_batch": args.batch, "decode_context": ctx,
+                 "decode_ms_per_step": round(sec * 1e3, 4), "decode_tokens_per_s": round(args.batch / sec, 1),
+                 "decode_launches_per_step": launches, "graph_replays": engine.runner.graph_replays,
+                 "weight_bytes_per_step": engine.model.weight_bytes()}
+            if not args.skip_points:
+                r["kernels"] = kernel_table(engine, names, PREFILL_TOKENS, args.batch, ctx, chunk, pk, extra={"ctx": ctx})
+            r["clocks"] = clocks.stop()
+            sampled.append(r["clocks"])
+            ops.check_kernel_status()
+            res[which] = r
+            del engine
+            torch.cuda.empty_cache()
+        out["sizes"][key] = res
+    seen = [c for c in sampled if c["sm_mhz"] is not None]
+    out["clocks"] = {"sm_mhz": min(c["sm_mhz"] for c in seen) if seen else None,
+                     "sm_max_mhz": max(c["sm_max_mhz"] for c in seen) if seen else None,
+                     "reasons": sorted({x for c in seen for x in c["reasons"]})}
+    print(json.dumps(out))
+    return 0
+
+
 # Kinds of launches that `--without` leaves out of a decode step, to see what each costs inside it.
 LEFT_OUT = ("norms", "rotation", "attention", "qkv", "o", "gate_up", "down", "head", "products")
 
@@ -854,12 +973,13 @@ def main() -> int:
     ap.add_argument("--without", default=None, choices=sorted(LEFT_OUT),
                     help="with --only decode: time the step with the launches of one kind left out (its results are "
                          "wrong; the difference to the full step is what that kind costs inside the step)")
-    ap.add_argument("--workload", default="headline", choices=["headline", "serving", "longctx", "notirax", "luzinex", "rabapel"],
+    ap.add_argument("--workload", default="headline", choices=["headline", "serving", "longctx", "notirax", "luzinex", "rabapel", "ledinex"],
                     help="serving: 64 requests on the 3B shape; longctx: 8 x 16,384 tokens on the 8B shape; notirax / "
                          "luzinex: prefill and decode of that design beside the Llama decoder at equal size, per kernel; "
-                         "rabapel: the same beside a Luzinex decoder of latent-attention layers at equal size")
+                         "rabapel: the same beside a Luzinex decoder of latent-attention layers at equal size; "
+                         "ledinex: the same beside a Notirax decoder at equal size")
     ap.add_argument("--size", default=None, choices=sorted(set(NOTIRAX_SIZES) | set(LUZINEX_SIZES) | set(RABAPEL_SIZES)),
-                    help="with --workload notirax, luzinex or rabapel: one size only")
+                    help="with --workload notirax, luzinex, rabapel or ledinex: one size only")
     args = ap.parse_args()
     args.shape_given = args.shape is not None
     args.shape = args.shape or "1b"
@@ -877,6 +997,8 @@ def main() -> int:
         return run_luzinex(args)
     if args.workload == "rabapel":
         return run_rabapel(args)
+    if args.workload == "ledinex":
+        return run_ledinex(args)
     if args.workload != "headline":
         return run_workload(args)
 

@@ -10,7 +10,7 @@
 // and h is rounded once.  The last taps-1 rows of x that a sequence's convolution has read are kept
 // in the request's state slot ([taps-1, H] at `tail_off`), so a step goes on from where the step
 // before ended however the tokens were cut; a second kernel moves them on after the first has read
-// them.  Both may be asked for the rows of a list only (the places whose logits are wanted).
+// them.
 #include "common.cuh"
 
 // ------------------------------------------------------------------ h = x + conv(x)
@@ -149,14 +149,65 @@ postnorm_add_kernel(float* __restrict__ x, int H, const T1* __restrict__ y1, flo
   for (int c = threadIdx.x; c < H; c += blockDim.x) x[t * H + c] += pn_y[c] * inv * g[c];
 }
 
+// four channels a thread with 16-byte accesses to the stream (H a multiple of 4): the sums stay in registers
+template <typename T1, int PER>
+__global__ void __launch_bounds__(256)
+postnorm_add_vec_kernel(float* __restrict__ x, int H, const T1* __restrict__ y1, float s1, const T1* __restrict__ y2,
+                        float s2, const float* __restrict__ g, float eps) {
+  __shared__ float red[32];
+  pdl_launch();
+  pdl_wait();
+  const long long t = blockIdx.x;
+  float y[PER][4];
+  float ss = 0.f;
+#pragma unroll
+  for (int p = 0; p < PER; p++) {
+    const int c = (p * 256 + threadIdx.x) * 4;
+#pragma unroll
+    for (int j = 0; j < 4; j++) y[p][j] = 0.f;
+    if (c < H) {
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        float v = s1 * to_f32<T1>(y1[t * H + c + j]);
+        if (y2) v = fmaf(s2, to_f32<T1>(y2[t * H + c + j]), v);
+        y[p][j] = v;
+        ss = fmaf(v, v, ss);
+      }
+    }
+  }
+  ss = block_sum(ss, red);
+  const float inv = 1.0f / sqrtf(ss / (float)H + eps);
+#pragma unroll
+  for (int p = 0; p < PER; p++) {
+    const int c = (p * 256 + threadIdx.x) * 4;
+    if (c < H) {
+      float4 xv = *reinterpret_cast<float4*>(x + t * H + c);
+      const float4 gv = *reinterpret_cast<const float4*>(g + c);
+      xv.x += y[p][0] * inv * gv.x;
+      xv.y += y[p][1] * inv * gv.y;
+      xv.z += y[p][2] * inv * gv.z;
+      xv.w += y[p][3] * inv * gv.w;
+      *reinterpret_cast<float4*>(x + t * H + c) = xv;
+    }
+  }
+}
+
 MF_API int mf_postnorm_add(float* x, int T, int H, const void* y1, float s1, const void* y2, float s2, int y_dtype,
                            const float* g, float eps, cudaStream_t stream) {
   if (T <= 0) return 0;
   const size_t smem = (size_t)H * sizeof(float);
   if (H <= 0 || smem > 200 * 1024) return MF_ERR_BAD_ARG;
   mf_count(MF_K_POSTNORM_ADD);
+  const bool vec = H % 4 == 0 && H <= 8 * 1024 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)g & 15) == 0;
+#define PN_VEC(T1, PER)                                                                                           \
+  return (int)launch_dep(postnorm_add_vec_kernel<T1, PER>, dim3(T), dim3(256), 0, stream, x, H, (const T1*)y1, s1, \
+                         (const T1*)y2, s2, g, eps)
 #define PN_LAUNCH(T1)                                                                                             \
   do {                                                                                                            \
+    if (vec && H <= 1024) PN_VEC(T1, 1);                                                                          \
+    if (vec && H <= 2048) PN_VEC(T1, 2);                                                                          \
+    if (vec && H <= 4096) PN_VEC(T1, 4);                                                                          \
+    if (vec) PN_VEC(T1, 8);                                                                                       \
     if (smem > 48 * 1024) {                                                                                       \
       cudaError_t e = cudaFuncSetAttribute(postnorm_add_kernel<T1>, cudaFuncAttributeMaxDynamicSharedMemorySize,  \
                                            (int)smem);                                                            \
@@ -168,5 +219,6 @@ MF_API int mf_postnorm_add(float* x, int T, int H, const void* y1, float s1, con
   if (y_dtype == MF_F32) PN_LAUNCH(float);
   if (y_dtype == MF_BF16) PN_LAUNCH(__nv_bfloat16);
 #undef PN_LAUNCH
+#undef PN_VEC
   return MF_ERR_BAD_DTYPE;
 }

@@ -5,10 +5,18 @@ tensors and its own cache need; the pair's need is the tuple of both (a branch w
 entry) and the pair hands each branch its own lanes.  The two outputs are not added here: they travel
 on as a ``ScaledPair`` so that whoever takes them (the norm on the sublayer's output) forms the weighted
 sum in 32-bit in the kernel it runs anyway.
+
+The branches depend on nothing of each other.  With many tokens in a step (``overlap_min_tokens``, 256 by
+default; 0 switches it off) the right branch is launched on a second stream, forked from and joined back to
+the step's stream by events, so that a branch whose kernels fill a fraction of the GPU (a recurrence that is
+serial in time) runs beside the other's products and attention instead of before them.  Steps of few
+tokens (decoding, which is replayed from CUDA graphs) stay on one stream.
 """
 from __future__ import annotations
 
 from typing import Dict
+
+import torch
 
 from .base import MIXERS, Mixer, ScaledPair, TensorSpec, build_part, count_needs, flatten_needs, register_mixer
 
@@ -23,6 +31,8 @@ class SideBySide(Mixer):
         self.right_scale = float(params.get("right_scale", 1.0))
         self.n_left = count_needs(self.left.cache_need())
         self.n_right = count_needs(self.right.cache_need())
+        self.overlap_min_tokens = int(params.get("overlap_min_tokens", 256))
+        self._side = self._fork = self._join = None
 
     @property
     def graph_safe(self) -> bool:
@@ -50,6 +60,19 @@ class SideBySide(Mixer):
 
     def forward(self, x, batch, cache, writes_cache: bool = True):
         lanes = cache if isinstance(cache, tuple) else (() if cache is None else (cache,))
-        y1 = self.left.forward(x, batch, self._lanes(lanes, 0, self.n_left), writes_cache)
-        y2 = self.right.forward(x, batch, self._lanes(lanes, self.n_left, self.n_right), writes_cache)
+        left_lanes, right_lanes = self._lanes(lanes, 0, self.n_left), self._lanes(lanes, self.n_left, self.n_right)
+        if not (self.overlap_min_tokens and x.shape[0] >= self.overlap_min_tokens and x.is_cuda):
+            y1 = self.left.forward(x, batch, left_lanes, writes_cache)
+            y2 = self.right.forward(x, batch, right_lanes, writes_cache)
+            return ScaledPair(y1, self.left_scale, y2, self.right_scale)
+        if self._side is None:
+            self._side, self._fork, self._join = torch.cuda.Stream(), torch.cuda.Event(), torch.cuda.Event()
+        main = torch.cuda.current_stream()
+        self._fork.record(main)                       # x and everything before it are ready for the side stream
+        self._side.wait_event(self._fork)
+        with torch.cuda.stream(self._side):
+            y2 = self.right.forward(x, batch, right_lanes, writes_cache)
+            self._join.record(self._side)
+        y1 = self.left.forward(x, batch, left_lanes, writes_cache)
+        main.wait_event(self._join)                   # whoever takes the pair reads both
         return ScaledPair(y1, self.left_scale, y2, self.right_scale)
