@@ -10,7 +10,7 @@ Mixer keys.  ``parallel`` and ``parallel_2``: ``left`` (attention: ``heads, kv_h
 ``softcap``, ``mask.size``, ``rot.{base, dims, scaling}`` with ``scaling.factor`` alone or with
 ``original, fast, slow``), ``right`` (``heads, dim``, and for ``parallel`` ``vdim`` and ``decay``, one per head),
 ``left_scale``, ``right_scale``.  ``delta``: ``heads, kv_heads, dim, vdim, conv``.  What a file may leave out:
-``embedding.scale`` (1), ``logit_scale`` (1), ``canon`` (one tap: no neighbours), ``kv_heads`` (``heads``),
+``embedding.scale`` (1), ``logit_scale`` (1), ``canon`` (no convolution and no ``canon*`` tensors), ``kv_heads`` (``heads``),
 ``vdim`` (``dim``), ``scale`` (``dim^-1/2``), ``softcap`` (none), ``mask`` (causal), ``rot`` (no rotation),
 ``rot.dims`` (``dim``), ``rot.scaling`` (plain frequencies), the two scales (1), ``shared`` (no shared expert).
 The low rank of a ``parallel_2`` layer's decay is not in config.json: it is the first extent of the tensor
@@ -132,7 +132,7 @@ class LedinexConfig(ModelConfig):
     norm_eps: float = 0.0
     embedding_scale: float = 1.0
     logit_scale: float = 1.0
-    taps: int = 1
+    taps: int = 0          # 0: the file has no ``canon``: sublayers read the stream as it is
     # per layer: {"type", "mixer": {...}, "mlp": {...} | None}, parsed and checked
     layers: Tuple[Dict[str, Any], ...] = field(default=(), compare=False)
 
@@ -149,7 +149,8 @@ class LedinexConfig(ModelConfig):
         scale = _finite(_opt(_obj(j, "embedding", "", required=False), "scale", float, 1.0, "embedding."),
                         "embedding.scale")
         logit_scale = _finite(_opt(j, "logit_scale", float, 1.0, ""), "logit_scale")
-        taps = _positive(_opt(_obj(j, "canon", "", required=False), "taps", int, 1, "canon."), "canon.taps")
+        canon = _obj(j, "canon", "", required=False)
+        taps = _positive(_req(canon, "taps", int, "canon."), "canon.taps") if canon else 0
         raw_layers = j.get("layers")
         if not isinstance(raw_layers, list) or not raw_layers:
             raise ConfigError("config.json: missing required field 'layers' (a list of layers)")
@@ -186,7 +187,9 @@ class LedinexConfig(ModelConfig):
         """The config.json this configuration would be read back from."""
         out: Dict[str, Any] = {"architecture": self.architecture, "vocab": self.vocab, "width": self.width,
                                "norm": {"eps": self.norm_eps}, "embedding": {"scale": self.embedding_scale},
-                               "logit_scale": self.logit_scale, "canon": {"taps": self.taps}, "layers": []}
+                               "logit_scale": self.logit_scale, "layers": []}
+        if self.taps:
+            out["canon"] = {"taps": self.taps}
         for layer in self.layers:
             m = layer["mixer"]
             if layer["type"] == "delta":

@@ -105,7 +105,8 @@ def ledinex_random_tensors(cfg: LedinexConfig) -> Iterator[Tuple[str, Tuple[int,
     for i, layer in enumerate(cfg.layers):
         p, m, kind = f"l{i}.", layer["mixer"], layer["type"]
         yield p + "norm1", (H,), (0.0, 0.1)
-        yield p + "canon1", (H, cfg.taps), (0.0, 0.2)
+        if cfg.taps:
+            yield p + "canon1", (H, cfg.taps), (0.0, 0.2)
         if kind == "delta":
             nqk, nv, nh = m["kv_heads"] * m["dim"], m["heads"] * m["vdim"], m["heads"]
             for r, n in (("q", nqk), ("k", nqk), ("v", nv)):
@@ -156,7 +157,8 @@ def ledinex_random_tensors(cfg: LedinexConfig) -> Iterator[Tuple[str, Tuple[int,
         if mlp is None:
             continue
         yield p + "norm2", (H,), (0.0, 0.1)
-        yield p + "canon2", (H, cfg.taps), (0.0, 0.2)
+        if cfg.taps:
+            yield p + "canon2", (H, cfg.taps), (0.0, 0.2)
         yield p + "mlp.router", (mlp["experts"], H), "matrix"
         for e in range(mlp["experts"]):
             yield p + f"mlp.e{e}.up", (mlp["ff"], H), "matrix"

@@ -79,8 +79,12 @@ class ConvRead(Connection):
         self.size = int(params["size"])
         self.taps = int(params["taps"])
         self.name = self.prefix + str(params.get("tensor", "conv"))
+        # taps 0: no convolution and no tensor; the sublayer reads the stream's rounding (one tap of weight zero)
+        self.identity = self.taps == 0
+        if self.identity:
+            self.taps = 1
         if self.taps < 1:
-            raise ValueError(f"conv_read: {self.taps} taps (at least 1)")
+            raise ValueError(f"conv_read: {self.taps} taps (0 for none, else at least 1)")
         self.weight = None
 
     @property
@@ -89,10 +93,13 @@ class ConvRead(Connection):
         return (self.taps - 1) * self.size
 
     def tensor_specs(self) -> Dict[str, TensorSpec]:
-        return {self.name: TensorSpec((self.size, self.taps), role="vector")}
+        return {} if self.identity else {self.name: TensorSpec((self.size, self.taps), role="vector")}
 
     def bind(self, tensors) -> None:
-        self.weight = tensors[self.name].to(torch.float32).contiguous()
+        if self.identity:
+            self.weight = torch.zeros((self.size, 1), dtype=torch.float32, device=self.rt.device)
+        else:
+            self.weight = tensors[self.name].to(torch.float32).contiguous()
 
     def weight_bytes(self) -> int:
         return self.size * self.taps * 4

@@ -65,7 +65,7 @@ LX_A = {"architecture": "Ledinex", "vocab": 101, "width": 40, "norm": {"eps": 1e
                    _with(_par2(_attn(2, 1, 20, 20, 0.2, _rot(90.0, 20, (2.5, 24, 3.0, 0.5)), window=37), 1, 14, 3, 0.5, 1.1),
                          _moe(12, 4, 1, shared=8)),
                    _with(_delta(3, 3, 10, 4, 2), _moe(8, 6, 2))]}
-# everything that can be 1, equal or absent: one tap (no neighbours), scales of 1, one head, equal head sizes,
+# everything that can be 1, equal or absent: no convolution on the inputs, scales of 1, one head, equal head sizes,
 # a window of one token and one of exactly a page, no soft cap, no rotation in one layer, a factor of 1, one
 # expert, decays of 1 and 0, a convolution of one tap in the delta mixer
 LX_B = {"architecture": "Ledinex", "vocab": 64, "width": 32, "norm": {"eps": 1e-6},
@@ -134,15 +134,15 @@ def random_config(seed, big):
         layers.append(_with(layer(), mlp))
     return {"architecture": "Ledinex", "vocab": int(pick([50, 101, 256, 1000])), "width": width,
             "norm": {"eps": float(pick([1e-6, 1e-5]))}, "embedding": {"scale": float(pick([1.0, 4.0, 16.0]))},
-            "logit_scale": float(pick([1.0, 2.0, 0.3])), "canon": {"taps": int(pick([1, 2, 3, 4]))}, "layers": layers}
+            "logit_scale": float(pick([1.0, 2.0, 0.3])), **({"canon": {"taps": int(pick([1, 2, 3, 4]))}} if rng.random() < 0.9 else {}), "layers": layers}
 
 
 def tensor_shapes(cfg):
-    H, taps = cfg["width"], (cfg.get("canon") or {}).get("taps", 1)
+    H, taps = cfg["width"], (cfg.get("canon") or {}).get("taps", 0)      # no canon: no convolution, no tensors
     out = [("embed", (cfg["vocab"], H))]
     for i, layer in enumerate(cfg["layers"]):
         p, m, kind = f"l{i}.", layer["mixer"], layer["type"]
-        out += [(p + "norm1", (H,)), (p + "canon1", (H, taps))]
+        out += [(p + "norm1", (H,))] + ([(p + "canon1", (H, taps))] if taps else [])
         if kind == "delta":
             nqk, nv, nh = m["kv_heads"] * m["dim"], m["heads"] * m["vdim"], m["heads"]
             out += [(p + "mix.q", (nqk, H)), (p + "mix.q.conv", (nqk, m["conv"])), (p + "mix.k", (nqk, H)),
@@ -170,7 +170,8 @@ def tensor_shapes(cfg):
         mlp = layer["mlp"]
         if mlp is None:
             continue
-        out += [(p + "norm2", (H,)), (p + "canon2", (H, taps)), (p + "mlp.router", (mlp["router"]["experts"], H))]
+        out += [(p + "norm2", (H,))] + ([(p + "canon2", (H, taps))] if taps else [])
+        out += [(p + "mlp.router", (mlp["router"]["experts"], H))]
         ff = mlp["expert"]["ff"]
         for e in range(mlp["router"]["experts"]):
             out += [(p + f"mlp.e{e}.up", (ff, H)), (p + f"mlp.e{e}.down", (H, ff))]

@@ -349,10 +349,10 @@ def forward(config, tensors, tokens, layers_out=None, choices_out=None):
     x = E[np.asarray(tokens)] * float((config.get("embedding") or {}).get("scale", 1.0))
     for i, layer in enumerate(config["layers"]):
         p = f"l{i}."
-        h = _r(input_convolution(x, tensors[p + "canon1"]))      # a file without taps has one: [width, 1]
+        h = _r(input_convolution(x, tensors[p + "canon1"]) if p + "canon1" in tensors else x)
         x = x + norm_one_plus(mixer_forward(h, layer, _sub(tensors, p + "mix."), eps), tensors[p + "norm1"], eps)
         if layer.get("mlp"):
-            h = _r(input_convolution(x, tensors[p + "canon2"]))
+            h = _r(input_convolution(x, tensors[p + "canon2"]) if p + "canon2" in tensors else x)
             W = _sub(tensors, p + "mlp.")
             x = x + norm_one_plus(mixture(h, W, layer["mlp"]), tensors[p + "norm2"], eps)
             if choices_out is not None:

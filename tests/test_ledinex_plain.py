@@ -213,7 +213,7 @@ def test_config_reader_defaults_errors_and_round_trip():
     from mlxforge_b200.config.registry import registered_architectures
     assert "Ledinex" in registered_architectures()
     c = config_from_json(json.loads(json.dumps(LX_B)))
-    assert (c.taps, c.embedding_scale, c.logit_scale) == (1, 1.0, 1.0)
+    assert (c.taps, c.embedding_scale, c.logit_scale) == (0, 1.0, 1.0)
     left = c.layers[0]["mixer"]["left"]
     assert left["rot"] is None and left["window"] == 0 and left["softcap"] == 0.0
     assert c.layers[4]["mixer"]["left"]["rot"]["scaling"] == {"factor": 1.0}
