@@ -10,22 +10,23 @@
 // and h is rounded once.  The last taps-1 rows of x that a sequence's convolution has read are kept
 // in the request's state slot ([taps-1, H] at `tail_off`), so a step goes on from where the step
 // before ended however the tokens were cut; a second kernel moves them on after the first has read
-// them.
+// them.  Where every sequence of the step brings one token (decoding) a token's block is the only reader
+// of its slot's rows and moves them on itself: one launch.
 #include "common.cuh"
 
 // ------------------------------------------------------------------ h = x + conv(x)
 template <typename TO>
 __global__ void __launch_bounds__(256)
 conv_input_kernel(const float* __restrict__ x, int H, const float* __restrict__ w, int taps,
-                  const float* __restrict__ state, long long state_stride, long long tail_off,
+                  float* __restrict__ state, long long state_stride, long long tail_off,
                   const int* __restrict__ seq_of_token, const int* __restrict__ seq_q_start,
-                  const int* __restrict__ slots, TO* __restrict__ out) {
+                  const int* __restrict__ slots, TO* __restrict__ out, int move_tail) {
   pdl_launch();
   pdl_wait();
   const int t = blockIdx.x;
   const int seq = seq_of_token[t];
   const int rel = t - seq_q_start[seq];
-  const float* tail = state + (long long)slots[seq] * state_stride + tail_off;      // [(taps-1), H]
+  float* tail = state + (long long)slots[seq] * state_stride + tail_off;      // [(taps-1), H]
   for (int c = threadIdx.x; c < H; c += blockDim.x) {
     float a = 0.f;
     for (int j = 0; j < taps; j++) {
@@ -34,6 +35,9 @@ conv_input_kernel(const float* __restrict__ x, int H, const float* __restrict__ 
       a = fmaf(w[(long long)c * taps + j], v, a);
     }
     out[(long long)t * H + c] = from_f32<TO>(x[(long long)t * H + c] + a);
+    if (move_tail)          // the sequence's only token: every row moves up one place, the token's row comes last
+      for (int j = 0; j < taps - 1; j++)
+        tail[(long long)j * H + c] = j < taps - 2 ? tail[(long long)(j + 1) * H + c] : x[(long long)t * H + c];
   }
 }
 
@@ -41,23 +45,25 @@ conv_input_kernel(const float* __restrict__ x, int H, const float* __restrict__ 
 template <typename TO, int TAPS>
 __global__ void __launch_bounds__(256)
 conv_input_vec_kernel(const float* __restrict__ x, int H, const float* __restrict__ w,
-                      const float* __restrict__ state, long long state_stride, long long tail_off,
+                      float* __restrict__ state, long long state_stride, long long tail_off,
                       const int* __restrict__ seq_of_token, const int* __restrict__ seq_q_start,
-                      const int* __restrict__ slots, TO* __restrict__ out) {
+                      const int* __restrict__ slots, TO* __restrict__ out, int move_tail) {
   pdl_launch();
   pdl_wait();
   const int t = blockIdx.x;
   const int seq = seq_of_token[t];
   const int rel = t - seq_q_start[seq];
-  const float* tail = state + (long long)slots[seq] * state_stride + tail_off;
+  float* tail = state + (long long)slots[seq] * state_stride + tail_off;
   for (int c = threadIdx.x * 4; c < H; c += blockDim.x * 4) {
     float a[4] = {0.f, 0.f, 0.f, 0.f};
     float4 cur = make_float4(0.f, 0.f, 0.f, 0.f);
+    float4 seen[TAPS];
 #pragma unroll
     for (int j = 0; j < TAPS; j++) {
       const int back = TAPS - 1 - j;
       const float4 v = rel - back >= 0 ? *reinterpret_cast<const float4*>(x + (long long)(t - back) * H + c)
                                        : *reinterpret_cast<const float4*>(tail + (long long)(rel - back + TAPS - 1) * H + c);
+      seen[j] = v;
       if (back == 0) cur = v;
       a[0] = fmaf(w[(long long)(c + 0) * TAPS + j], v.x, a[0]);
       a[1] = fmaf(w[(long long)(c + 1) * TAPS + j], v.y, a[1]);
@@ -69,6 +75,10 @@ conv_input_vec_kernel(const float* __restrict__ x, int H, const float* __restric
     o[1] = from_f32<TO>(cur.y + a[1]);
     o[2] = from_f32<TO>(cur.z + a[2]);
     o[3] = from_f32<TO>(cur.w + a[3]);
+    if (move_tail) {        // the sequence's only token: what was read, one place on
+#pragma unroll
+      for (int j = 0; j < TAPS - 1; j++) *reinterpret_cast<float4*>(tail + (long long)j * H + c) = seen[j + 1];
+    }
   }
 }
 
@@ -98,27 +108,29 @@ MF_API int mf_conv_input(const float* x, int T, int H, const float* w, int taps,
   if (out_dtype != MF_F32 && out_dtype != MF_BF16) return MF_ERR_BAD_DTYPE;
   mf_count(MF_K_CONV_INPUT);
   cudaError_t e;
+  // one token from every sequence (the caller lays the step out so: T tokens of n_seqs sequences, none empty)
+  const int single = (T == n_seqs && taps > 1) ? 1 : 0;
   const bool vec = H % 4 == 0 && tail_off % 4 == 0 && state_stride % 4 == 0 && ((uintptr_t)x & 15) == 0 &&
                    ((uintptr_t)state & 15) == 0 && taps >= 2 && taps <= 4;
   const int threads = vec ? (H / 4 >= 256 ? 256 : ((H / 4 + 31) / 32) * 32) : 256;
 #define CI_VEC(TO, TAPS)                                                                                          \
-  e = launch_dep(conv_input_vec_kernel<TO, TAPS>, dim3(T), dim3(threads), 0, stream, x, H, w, (const float*)state, \
-                 state_stride, tail_off, seq_of_token, seq_q_start, slots, (TO*)out)
+  e = launch_dep(conv_input_vec_kernel<TO, TAPS>, dim3(T), dim3(threads), 0, stream, x, H, w, state, state_stride,  \
+                 tail_off, seq_of_token, seq_q_start, slots, (TO*)out, single)
 #define CI_ANY(TO)                                                                                                \
   do {                                                                                                            \
     if (vec && taps == 2) CI_VEC(TO, 2);                                                                          \
     else if (vec && taps == 3) CI_VEC(TO, 3);                                                                     \
     else if (vec && taps == 4) CI_VEC(TO, 4);                                                                     \
     else                                                                                                          \
-      e = launch_dep(conv_input_kernel<TO>, dim3(T), dim3(256), 0, stream, x, H, w, taps, (const float*)state,    \
-                     state_stride, tail_off, seq_of_token, seq_q_start, slots, (TO*)out);                         \
+      e = launch_dep(conv_input_kernel<TO>, dim3(T), dim3(256), 0, stream, x, H, w, taps, state, state_stride,    \
+                     tail_off, seq_of_token, seq_q_start, slots, (TO*)out, single);                               \
   } while (0)
   if (out_dtype == MF_F32) CI_ANY(float);
   else CI_ANY(__nv_bfloat16);
 #undef CI_ANY
 #undef CI_VEC
   if (e != cudaSuccess) return (int)e;
-  if (taps > 1) {
+  if (taps > 1 && !single) {
     const int by = (H + 1023) / 1024;
     e = launch_dep(conv_input_tail_kernel, dim3(n_seqs, by), dim3(256), 0, stream, x, H, taps, state, state_stride,
                    tail_off, seq_q_start, seq_q_len, slots);

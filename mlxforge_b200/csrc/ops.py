@@ -777,7 +777,8 @@ def conv_input(x: torch.Tensor, w: torch.Tensor, state: torch.Tensor, tail_off: 
     check(library().mf_conv_input(x.data_ptr(), T, H, w.data_ptr(), taps, state.data_ptr(), state.stride(0), tail_off,
                                   batch.seq_of_token.data_ptr(), batch.seq_q_start.data_ptr(),
                                   batch.seq_q_len.data_ptr(), batch.slots.data_ptr(), batch.n_seqs, out.data_ptr(),
-                                  dtype_code(out), _stream()), "conv_input", launches=2 if taps > 1 else 1)
+                                  dtype_code(out), _stream()), "conv_input",
+          launches=2 if taps > 1 and T != batch.n_seqs else 1)
 
 
 def postnorm_add(x: torch.Tensor, y1: torch.Tensor, s1: float, y2: Optional[torch.Tensor], s2: float,
