@@ -61,7 +61,9 @@ class SideBySide(Mixer):
     def forward(self, x, batch, cache, writes_cache: bool = True):
         lanes = cache if isinstance(cache, tuple) else (() if cache is None else (cache,))
         left_lanes, right_lanes = self._lanes(lanes, 0, self.n_left), self._lanes(lanes, self.n_left, self.n_right)
-        if not (self.overlap_min_tokens and x.shape[0] >= self.overlap_min_tokens and x.is_cuda):
+        # the opt-in products with scratch of their own (partial sums shared by all calls) stay on one stream
+        shared_scratch = getattr(self.rt, "mid_rows_enabled", False) or getattr(self.rt, "gemm_backend", "auto") == "tcgen05"
+        if shared_scratch or not (self.overlap_min_tokens and x.shape[0] >= self.overlap_min_tokens and x.is_cuda):
             y1 = self.left.forward(x, batch, left_lanes, writes_cache)
             y2 = self.right.forward(x, batch, right_lanes, writes_cache)
             return ScaledPair(y1, self.left_scale, y2, self.right_scale)

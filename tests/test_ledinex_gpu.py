@@ -447,7 +447,7 @@ def _replay(model_dir, dtype, trace, tmp_path, max_tokens=None, max_seqs=4):
     return out_dir, launched(before)
 
 
-def _judge(got, expected, tol_, dtype, close, what):
+def _compare(got, expected, tol_, dtype, close, what):
     assert got, "the trace asked for nothing"
     if dtype == "float32":
         got = {k: v for k, v in got.items() if k not in close}
@@ -457,18 +457,18 @@ def _judge(got, expected, tol_, dtype, close, what):
     # bfloat16: the limit is three times what rounding did to ONE run of the plain implementation, so a
     # place may pass it by chance; none passes one and a half times the limit and at most one place in
     # fifty (or one) passes the limit itself
-    judged = {k: v for k, v in got.items() if k not in close}
-    assert len(judged) >= 0.8 * len(got), "too many close calls for a test"
-    worst, where = TT.worst(judged, expected)
-    assert worst <= 1.5 * tol_, (what, worst, tol_, where, TT.first_bad(judged, expected, 1.5 * tol_))
-    over = sum(1 for (rid, pos), row in judged.items() if not np.max(np.abs(row.astype(np.float64) - expected[rid][pos])) <= tol_)
-    assert over <= max(1, len(judged) // 50), (what, over, len(judged), tol_, TT.first_bad(judged, expected, tol_))
+    kept = {k: v for k, v in got.items() if k not in close}
+    assert len(kept) >= 0.8 * len(got), "too many close calls for a test"
+    worst, where = TT.worst(kept, expected)
+    assert worst <= 1.5 * tol_, (what, worst, tol_, where, TT.first_bad(kept, expected, 1.5 * tol_))
+    over = sum(1 for (rid, pos), row in kept.items() if not np.max(np.abs(row.astype(np.float64) - expected[rid][pos])) <= tol_)
+    assert over <= max(1, len(kept) // 50), (what, over, len(kept), tol_, TT.first_bad(kept, expected, tol_))
 
 
 def _check(models, which, peaked, dtype, trace, tmp_path, **kw):
     d, cfg, reqs, expected, tols, _, close = models[(which, peaked)]
     out_dir, ran = _replay(d, dtype, trace, tmp_path, **kw)
-    _judge(TT.read_outputs(trace, out_dir, cfg["vocab"]), expected, tols[dtype], dtype, close[dtype], (which, peaked, dtype))
+    _compare(TT.read_outputs(trace, out_dir, cfg["vocab"]), expected, tols[dtype], dtype, close[dtype], (which, peaked, dtype))
     return ran
 
 
@@ -555,7 +555,7 @@ def test_configurations_drawn_at_random(seed, tmp_path):
             out_dir, _ = _replay(d, dtype, trace, tmp_path / f"{i}{dtype}", max_seqs=3 if i == 2 else 4)
             got = TT.read_outputs(trace, out_dir, cfg["vocab"])
             assert len(got) > 100
-            _judge(got, expected, tols[dtype], dtype, close[dtype], (cfg, i, dtype))
+            _compare(got, expected, tols[dtype], dtype, close[dtype], (cfg, i, dtype))
 
 
 def test_batch_and_cut_do_not_change_a_position(models, tmp_path):
