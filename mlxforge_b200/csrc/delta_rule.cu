@@ -617,45 +617,49 @@ gdelta_recurrence_kernel(const float* __restrict__ ops, const float* __restrict_
 
 // The same with the operands of the coming tokens brought into shared memory ahead of time, as the gated
 // rule's staged kernel does: stages of DR_CHUNK tokens (the r, k, u, a u and w rows of the head and the
-// block's 16 values) arrive by cp.async in a ring of DR_STAGES; channel d of a column belongs to lane
-// ((d / 4) % 8).  Needs dim and the row lengths to be multiples of 4 (16-byte copies).
-template <int DPT>
-__global__ void __launch_bounds__(DR_THREADS)
+// block's values) arrive by cp.async in a ring of DR_STAGES; LANES lanes share a column and COLS columns a
+// block; channel d of a column belongs to lane ((d / 4) % LANES).  A token's chain of instructions in a warp
+// is what bounds the kernel, so heads of more than 32 channels are spread over 16 lanes (fewer instructions a
+// lane and token) in blocks of 8 columns (less of the operands read again by every column).  Needs dim and
+// the row lengths to be multiples of 4 (16-byte copies).
+template <int DPT, int LANES, int COLS>
+__global__ void __launch_bounds__(LANES * COLS)
 gdelta_recurrence_staged_kernel(const float* __restrict__ ops, const float* __restrict__ w, int w_ld,
                                 const float* __restrict__ v, int v_ld, float* __restrict__ state,
                                 long long state_stride, const int* __restrict__ seq_q_start,
                                 const int* __restrict__ seq_q_len, const int* __restrict__ slots,
                                 float* __restrict__ o_out, int n_heads, int dim) {
-  constexpr int DP = DPT * DR_LANES;                         // channels, padded
-  constexpr int TOK = 5 * DP + DR_COLS;                      // floats of one token in a stage: r, k, u, au, w, v
+  constexpr int THREADS = LANES * COLS;
+  constexpr int DP = DPT * LANES;                         // channels, padded
+  constexpr int TOK = 5 * DP + COLS;                      // floats of one token in a stage: r, k, u, au, w, v
   extern __shared__ __align__(16) float gd_sm[];             // [DR_STAGES][DR_CHUNK][TOK]
   const int seq = blockIdx.x, h = blockIdx.y;
-  const int col0 = blockIdx.z * DR_COLS;
-  const int ci = threadIdx.x / DR_LANES, part = threadIdx.x % DR_LANES;
+  const int col0 = blockIdx.z * COLS;
+  const int ci = threadIdx.x / LANES, part = threadIdx.x % LANES;
   const int col = col0 + ci;
   const int n = n_heads * dim;
   const int start = seq_q_start[seq], len = seq_q_len[seq];
   const bool live = col < dim;
-  if (dim < DP || col0 + DR_COLS > dim) {                    // the padding is never copied: zero once
-    for (int i = threadIdx.x; i < DR_STAGES * DR_CHUNK * TOK; i += DR_THREADS) gd_sm[i] = 0.f;
+  if (dim < DP || col0 + COLS > dim) {                    // the padding is never copied: zero once
+    for (int i = threadIdx.x; i < DR_STAGES * DR_CHUNK * TOK; i += THREADS) gd_sm[i] = 0.f;
     __syncthreads();
   }
   float* S = state + (long long)slots[seq] * state_stride + (long long)h * dim * dim;
   float s[DPT];
 #pragma unroll
   for (int i = 0; i < DPT; i++) {
-    const int d = ((i >> 2) * DR_LANES + part) * 4 + (i & 3);
+    const int d = ((i >> 2) * LANES + part) * 4 + (i & 3);
     s[i] = (live && d < dim) ? S[(long long)d * dim + col] : 0.f;
   }
   const int d4 = dim / 4;
   const int n_chunks = (len + DR_CHUNK - 1) / DR_CHUNK;
   // what this thread copies of every stage, worked out once: 16-byte pieces of the five rows, one of the values
-  constexpr int NP = (DR_CHUNK * 5 * (DP / 4) + DR_THREADS - 1) / DR_THREADS;
+  constexpr int NP = (DR_CHUNK * 5 * (DP / 4) + THREADS - 1) / THREADS;
   const float* src[NP];
   int dst[NP], ptok[NP], pstep[NP];
 #pragma unroll
   for (int p = 0; p < NP; p++) {
-    const int i = threadIdx.x + p * DR_THREADS;
+    const int i = threadIdx.x + p * THREADS;
     ptok[p] = DR_CHUNK;                                   // no piece
     src[p] = ops;
     dst[p] = 0;
@@ -670,8 +674,8 @@ gdelta_recurrence_staged_kernel(const float* __restrict__ ops, const float* __re
       dst[p] = tok * TOK + which * DP + c;
     }
   }
-  const int vtok = threadIdx.x / (DR_COLS / 4), vc = (threadIdx.x % (DR_COLS / 4)) * 4;      // 32 threads: 8 tokens x 4 pieces
-  const bool vcopy = threadIdx.x < DR_CHUNK * (DR_COLS / 4) && col0 + vc < dim;
+  const int vtok = threadIdx.x / (COLS / 4), vc = (threadIdx.x % (COLS / 4)) * 4;      // 32 threads: 8 tokens x 4 pieces
+  const bool vcopy = threadIdx.x < DR_CHUNK * (COLS / 4) && col0 + vc < dim;
   const float* vsrc = v + (long long)(start + vtok) * v_ld + h * dim + col0 + vc;
   auto issue = [&](int chunk) {
     if (chunk < n_chunks) {
@@ -703,19 +707,19 @@ gdelta_recurrence_staged_kernel(const float* __restrict__ ops, const float* __re
       float dp[DPT / 4];
 #pragma unroll
       for (int i4 = 0; i4 < DPT / 4; i4++) {
-        const float4 u = u4[i4 * DR_LANES + part];
+        const float4 u = u4[i4 * LANES + part];
         dp[i4] = fmaf(s[4 * i4 + 3], u.w, fmaf(s[4 * i4 + 2], u.z, fmaf(s[4 * i4 + 1], u.y, s[4 * i4] * u.x)));
       }
       float dot = dp[0];
 #pragma unroll
       for (int i4 = 1; i4 < DPT / 4; i4++) dot += dp[i4];
 #pragma unroll
-      for (int off = 1; off < DR_LANES; off <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, off);
+      for (int off = 1; off < LANES; off <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, off);
       float op[DPT / 4];
 #pragma unroll
       for (int i4 = 0; i4 < DPT / 4; i4++) {
-        const float4 kk = k4[i4 * DR_LANES + part], au = a4[i4 * DR_LANES + part], ww = w4[i4 * DR_LANES + part];
-        const float4 r = r4[i4 * DR_LANES + part];
+        const float4 kk = k4[i4 * LANES + part], au = a4[i4 * LANES + part], ww = w4[i4 * LANES + part];
+        const float4 r = r4[i4 * LANES + part];
         s[4 * i4] = fmaf(kk.x, vc_, fmaf(-au.x, dot, ww.x * s[4 * i4]));
         s[4 * i4 + 1] = fmaf(kk.y, vc_, fmaf(-au.y, dot, ww.y * s[4 * i4 + 1]));
         s[4 * i4 + 2] = fmaf(kk.z, vc_, fmaf(-au.z, dot, ww.z * s[4 * i4 + 2]));
@@ -726,14 +730,14 @@ gdelta_recurrence_staged_kernel(const float* __restrict__ ops, const float* __re
 #pragma unroll
       for (int i4 = 1; i4 < DPT / 4; i4++) o += op[i4];
 #pragma unroll
-      for (int off = 1; off < DR_LANES; off <<= 1) o += __shfl_xor_sync(0xffffffffu, o, off);
+      for (int off = 1; off < LANES; off <<= 1) o += __shfl_xor_sync(0xffffffffu, o, off);
       if (live && part == 0) o_out[(long long)(start + chunk * DR_CHUNK + tok) * n + h * dim + col] = o;
     }
   }
   asm volatile("cp.async.wait_group 0;\n" ::: "memory");
 #pragma unroll
   for (int i = 0; i < DPT; i++) {
-    const int d = ((i >> 2) * DR_LANES + part) * 4 + (i & 3);
+    const int d = ((i >> 2) * LANES + part) * 4 + (i & 3);
     if (live && d < dim) S[(long long)d * dim + col] = s[i];
   }
 }
@@ -743,33 +747,34 @@ MF_API int mf_gdelta_recurrence(const float* ops, const float* w, int w_ld, cons
                                 float* o_out, int n_seqs, int n_heads, int dim, cudaStream_t stream) {
   if (n_seqs <= 0) return 0;
   if (dim <= 0 || dim > 16 * DR_LANES || n_heads <= 0 || n_heads > 65535) return MF_ERR_BAD_ARG;
-  dim3 grid(n_seqs, n_heads, (dim + DR_COLS - 1) / DR_COLS);
   mf_count(MF_K_GDELTA_RECURRENCE);
   const int per = (dim + DR_LANES - 1) / DR_LANES;
   const bool aligned = dim % 4 == 0 && w_ld % 4 == 0 && v_ld % 4 == 0 && ((uintptr_t)ops & 15) == 0 &&
                        ((uintptr_t)w & 15) == 0 && ((uintptr_t)v & 15) == 0;
   if (aligned) {
-#define GS_LAUNCH(DPT)                                                                                             \
+#define GS_LAUNCH(DPT, LANES, COLS)                                                                                \
   do {                                                                                                             \
-    const size_t smem = (size_t)DR_STAGES * DR_CHUNK * (5 * DPT * DR_LANES + DR_COLS) * sizeof(float);             \
+    const size_t smem = (size_t)DR_STAGES * DR_CHUNK * (5 * DPT * LANES + COLS) * sizeof(float);                   \
     static DeviceOnce once;                                                                                        \
     const int dev = mf_current_device();                                                                           \
     if (dev < 0) return MF_ERR_BAD_ARG;                                                                            \
     if (!once.done[dev]) {                                                                                         \
-      cudaError_t e = cudaFuncSetAttribute(gdelta_recurrence_staged_kernel<DPT>,                                   \
+      cudaError_t e = cudaFuncSetAttribute(gdelta_recurrence_staged_kernel<DPT, LANES, COLS>,                      \
                                            cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                \
       if (e != cudaSuccess) return (int)e;                                                                         \
       once.done[dev] = true;                                                                                       \
     }                                                                                                              \
-    gdelta_recurrence_staged_kernel<DPT><<<grid, DR_THREADS, smem, stream>>>(                                      \
+    const dim3 sgrid(n_seqs, n_heads, (dim + COLS - 1) / COLS);                                                    \
+    gdelta_recurrence_staged_kernel<DPT, LANES, COLS><<<sgrid, LANES * COLS, smem, stream>>>(                      \
         ops, w, w_ld, v, v_ld, state, state_stride, seq_q_start, seq_q_len, slots, o_out, n_heads, dim);           \
   } while (0)
-    if (per <= 4) GS_LAUNCH(4);
-    else if (per <= 8) GS_LAUNCH(8);
-    else GS_LAUNCH(16);
+    if (dim <= 32) GS_LAUNCH(4, 8, 16);
+    else if (dim <= 64) GS_LAUNCH(4, 16, 8);
+    else GS_LAUNCH(8, 16, 8);
 #undef GS_LAUNCH
     return (int)cudaGetLastError();
   }
+  dim3 grid(n_seqs, n_heads, (dim + DR_COLS - 1) / DR_COLS);
 #define GD_LAUNCH(DPT)                                                                                            \
   gdelta_recurrence_kernel<DPT><<<grid, DR_THREADS, 0, stream>>>(ops, w, w_ld, v, v_ld, state, state_stride,      \
                                                                  seq_q_start, seq_q_len, slots, o_out, n_heads, dim)
